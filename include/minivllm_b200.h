@@ -1,0 +1,109 @@
+/*
+ * minivllm_b200 — C ABI of the B200 (sm_100a) ragged-batch attention path.
+ *
+ * Every entry point is `extern "C"`, takes plain device pointers, sizes and a
+ * CUDA stream handle (a `cudaStream_t` passed as `void*`), launches on that
+ * stream without synchronising the host, and returns an `int` status:
+ * 0 = launched, non-zero = rejected before any launch (see mv_status).
+ * The library allocates no device memory on these paths and keeps no pointer
+ * after a call returns; the caller owns inputs, outputs and scratch.
+ *
+ * Each declaration cites the function of the reference engine
+ * (Wenyueh/MinivLLM, paths relative to that project) whose work it does.
+ */
+#ifndef MINIVLLM_B200_H
+#define MINIVLLM_B200_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* Element types of q/k/v and of a non-quantised cache. */
+enum mv_dtype { MV_F16 = 0, MV_BF16 = 1 };
+
+enum mv_status {
+  MV_OK = 0,
+  MV_ERR_NULL = 1,        /* a required pointer is null */
+  MV_ERR_ALIGN = 2,       /* a pointer or stride breaks the 16-byte rule */
+  MV_ERR_SHAPE = 3,       /* unsupported head_dim / head ratio / negative size */
+  MV_ERR_WORKSPACE = 4,   /* scratch buffer too small */
+  MV_ERR_DTYPE = 5,
+  MV_ERR_CUDA = 6,        /* the launch itself reported an error */
+  MV_ERR_LIMIT = 7        /* size beyond a documented fixed maximum */
+};
+
+/* Text of the last non-zero status returned on the calling thread. */
+const char* mv_last_error_string(void);
+
+/* Library version, bumped when a signature changes. */
+int mv_abi_version(void);
+
+/*
+ * Scatter new K/V rows into the paged cache.
+ * Replaces: src/myvllm/layers/attention.py:67-108 `store_kvcache` and its
+ * Triton kernel :7-64.  For every token t with slot_mapping[t] >= 0:
+ *   k_cache[slot_mapping[t]] = key[t],  v_cache[slot_mapping[t]] = value[t]
+ * with the cache seen as (num_slots, num_kv_heads, head_dim); slot -1 (any
+ * negative) is skipped.  key/value are (num_tokens, num_kv_heads, head_dim)
+ * with an arbitrary token stride (in elements) so the split view of a fused
+ * qkv projection needs no copy; heads and head_dim are contiguous.
+ *
+ * When k_scale and v_scale are non-null the caches hold int8 codes and the
+ * scatter is fused with per-token-per-head symmetric quantisation (no
+ * counterpart in the reference, which has no quantisation):
+ *   amax = max|x| over head_dim (fp32); s = float(fp16(amax / 127));
+ *   code = clamp(rint(x / s), -127, 127), 0 when s == 0;
+ * codes go to (num_slots, num_kv_heads, head_dim) int8 and s, as fp16, to
+ * (num_slots, num_kv_heads).
+ */
+int mv_store_kvcache(const void* key, const void* value,
+                     int64_t k_stride_tok, int64_t v_stride_tok,
+                     void* k_cache, void* v_cache,
+                     void* k_scale, void* v_scale,
+                     const int64_t* slot_mapping,
+                     int64_t num_tokens, int64_t num_slots,
+                     int num_kv_heads, int head_dim,
+                     int dtype, void* stream);
+
+/*
+ * Bytes of scratch mv_paged_decode needs for the given problem (split-K
+ * partial results); depends on shapes only, never on context_lens values.
+ * Returns -1 for an invalid shape.
+ */
+int64_t mv_paged_decode_workspace_bytes(int batch, int num_heads,
+                                        int num_kv_heads, int head_dim,
+                                        int max_blocks, int block_size);
+
+/*
+ * One-query-per-sequence attention over the paged cache.
+ * Replaces: src/myvllm/layers/attention.py:418-473 `paged_attention_decode`
+ * and its Triton kernel :283-415.  For sequence b and query head h:
+ *   out[b,h] = softmax_j(scale * q[b,h] . K[b,j,h/G]) . V[b,j,h/G],  j < context_lens[b]
+ * where token j lives at cache[block_tables[b, j / block_size], j % block_size]
+ * and G = num_heads / num_kv_heads.  Tokens whose table entry is negative
+ * get zero weight; a row with no live token writes zeros.
+ * q/out are (batch, num_heads, head_dim) contiguous; caches are
+ * (num_blocks, block_size, num_kv_heads, head_dim) contiguous, of `dtype`,
+ * or int8 codes with fp16 scales (num_blocks, block_size, num_kv_heads)
+ * when k_scale/v_scale are non-null.  block_tables is (batch, max_blocks)
+ * int32 with row stride bt_stride; context_lens is int32 or int64 and is
+ * clamped to [0, max_blocks * block_size].
+ * The grid depends on shapes only, so the call can be captured in a graph.
+ */
+int mv_paged_decode(void* out, const void* q,
+                    const void* k_cache, const void* v_cache,
+                    const void* k_scale, const void* v_scale,
+                    const int32_t* block_tables, int64_t bt_stride,
+                    int max_blocks,
+                    const void* context_lens, int ctx_is_i64,
+                    int batch, int num_heads, int num_kv_heads, int head_dim,
+                    int block_size, int64_t num_blocks, float scale,
+                    void* workspace, int64_t workspace_bytes,
+                    int dtype, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* MINIVLLM_B200_H */

@@ -1,0 +1,499 @@
+// Paged decode attention: one query token per sequence against a paged KV
+// cache, split over the KV length, sharing each KV read between the query
+// heads of a GQA group.
+//
+// Does the work of src/myvllm/layers/attention.py:283-473 of the reference
+// (one Triton program per (sequence, query head), scalar per-token loops, no
+// split, KV re-read per query head).  Design here:
+//   * work item = (sequence, KV chunk, KV head).  The chunk length is chosen
+//     on the device from sum(context_lens) so that the machine is filled
+//     whatever the batch looks like; the grid is persistent and depends on
+//     shapes only (graph-capturable).  Every CTA recomputes the same plan.
+//   * a CTA is 4 independent warps.  Each warp streams its own 16-token tiles
+//     of K and V through a private cp.async ring in shared memory (XOR-swizzled
+//     16-byte chunks, conflict-free for ldmatrix), so the main loop has no
+//     block-wide barrier and ~64 KB per CTA is in flight.
+//   * the G query heads of the KV head are the (zero-padded) 16 rows of an
+//     m16n8k16 MMA: S = Q K^T and O += P V run on the tensor cores with fp32
+//     accumulation, softmax statistics in fp32 registers, exp2 domain.
+//   * warps merge through shared memory; a sequence with one chunk writes its
+//     output directly, otherwise partial (m, l, O) go to the caller's scratch
+//     and a small combine kernel reduces them in a fixed order.
+// HBM-bound: algorithmic bytes = sum(ctx) * num_kv_heads * head_dim * 2 *
+// sizeof(elem) + q and out.
+#include "common.cuh"
+#include "mma.cuh"
+
+namespace mv {
+
+constexpr int kDecWarps = 4;
+constexpr int kDecThreads = kDecWarps * 32;
+constexpr int kDecStages = 3;
+constexpr int kTileTok = 16;                    // tokens per warp tile
+constexpr int kCtaTok = kTileTok * kDecWarps;   // tokens per CTA step
+constexpr int kChunkMax = 2048;                 // longest KV chunk of one work item
+constexpr int kDecCtasPerSM = 2;
+constexpr int kDecWaves = 2;                    // work items aimed at per resident CTA
+constexpr float kNegBig = -1e30f;               // finite "minus infinity" for running maxima
+
+struct DecodeParams {
+  void* out;
+  const void* q;
+  const void* k_cache;
+  const void* v_cache;
+  const int32_t* block_tables;
+  int64_t bt_stride;
+  int max_blocks;
+  const void* context_lens;
+  int ctx_is_i64;
+  int batch, num_heads, num_kv_heads, group, mtiles;
+  int block_size;
+  int64_t num_blocks;
+  float scale_log2;
+  int target_items;
+  int2* binfo;      // per sequence: (first item, number of items)
+  float* part_ml;   // (item, head, 2)
+  float* part_o;    // (item, head, D)
+};
+
+// Work items aimed at per (KV head, row tile): enough to give every resident
+// CTA kDecWaves items.  Shapes only, so host and device agree.
+__host__ __device__ inline int decode_target_items(int num_kv_heads, int mtiles) {
+  const int t = (kNumSMs * kDecCtasPerSM * kDecWaves) / (num_kv_heads * mtiles);
+  return t < 1 ? 1 : t;
+}
+__host__ __device__ inline int64_t decode_items_max(int batch, int num_kv_heads, int mtiles, int max_blocks,
+                                                    int block_size) {
+  const int64_t lmax = static_cast<int64_t>(max_blocks) * block_size;
+  int64_t per_seq = (lmax + kChunkMax - 1) / kChunkMax;
+  if (per_seq < 1) per_seq = 1;
+  return decode_target_items(num_kv_heads, mtiles) + static_cast<int64_t>(batch) * per_seq;
+}
+
+__device__ __forceinline__ int load_ctx(const DecodeParams& p, int b) {
+  long long c = p.ctx_is_i64 ? static_cast<const long long*>(p.context_lens)[b]
+                             : static_cast<long long>(static_cast<const int*>(p.context_lens)[b]);
+  const long long lim = static_cast<long long>(p.max_blocks) * p.block_size;
+  c = c < 0 ? 0 : (c > lim ? lim : c);
+  return static_cast<int>(c);
+}
+
+// Every CTA builds the same plan: chunk length and s_start[b] = first item of
+// sequence b (s_start[batch] = number of items).  Returns the chunk length.
+__device__ int build_plan(const DecodeParams& p, int* s_start, long long* s_red) {
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  long long sum = 0;
+  for (int b = tid; b < p.batch; b += kDecThreads) sum += load_ctx(p, b);
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, off);
+  if (lane == 0) s_red[warp] = sum;
+  __syncthreads();
+  long long total = 0;
+#pragma unroll
+  for (int w = 0; w < kDecWarps; ++w) total += s_red[w];
+  long long chunk = (total + p.target_items - 1) / p.target_items;
+  chunk = ((chunk + kCtaTok - 1) / kCtaTok) * kCtaTok;
+  if (chunk < kCtaTok) chunk = kCtaTok;
+  if (chunk > kChunkMax) chunk = kChunkMax;
+  const int ch = static_cast<int>(chunk);
+  __syncthreads();  // s_red is reused below
+
+  int carry = 0;
+  if (tid == 0) s_start[0] = 0;
+  for (int base = 0; base < p.batch; base += kDecThreads) {
+    const int b = base + tid;
+    int n = 0;
+    if (b < p.batch) {
+      n = (load_ctx(p, b) + ch - 1) / ch;
+      if (n < 1) n = 1;  // an empty sequence still owns one item, which writes zeros
+    }
+    int incl = n;
+#pragma unroll
+    for (int off = 1; off < 32; off <<= 1) {
+      const int v = __shfl_up_sync(0xffffffffu, incl, off);
+      if (lane >= off) incl += v;
+    }
+    if (lane == 31) s_red[warp] = incl;
+    __syncthreads();
+    int wofs = 0, tot = 0;
+#pragma unroll
+    for (int w = 0; w < kDecWarps; ++w) {
+      const int v = static_cast<int>(s_red[w]);
+      if (w < warp) wofs += v;
+      tot += v;
+    }
+    if (b < p.batch) s_start[b + 1] = carry + wofs + incl;
+    carry += tot;
+    __syncthreads();
+  }
+  return ch;
+}
+
+template <typename T, int D>
+struct DecodeSmem {
+  static constexpr int kRowBytes = D * 2;
+  static constexpr int kTileBytes = kTileTok * kRowBytes;          // one K or V tile
+  static constexpr int kStageBytes = 2 * kTileBytes;               // K then V
+  static constexpr int kWarpBytes = kDecStages * kStageBytes;
+  static constexpr int kRingBytes = kDecWarps * kWarpBytes;
+  static constexpr int kMergeStride = D + 8;                       // floats per merged row
+  static constexpr int kMergeBytes = kDecWarps * 16 * kMergeStride * 4 + kDecWarps * 16 * 2 * 4;
+  static_assert(kMergeBytes <= kRingBytes, "merge buffer must fit in the ring");
+};
+
+template <typename T, int D>
+__global__ void __launch_bounds__(kDecThreads, kDecCtasPerSM)
+paged_decode_kernel(const DecodeParams p) {
+  using S = DecodeSmem<T, D>;
+  constexpr int CPR = D / 8;              // 16-byte chunks per row
+  constexpr int RPI = 32 / CPR;           // rows covered by one warp-wide cp.async
+  constexpr int LOAD_ITERS = kTileTok / RPI;
+  constexpr int KSTEPS = D / 16;
+  constexpr int NT = D / 8;               // output n-tiles
+
+  extern __shared__ __align__(128) unsigned char smem[];
+  __shared__ long long s_red[kDecWarps];
+  __shared__ uint32_t s_mask[kDecWarps][kDecStages];
+  int* s_start = reinterpret_cast<int*>(smem + S::kRingBytes);
+
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int g = lane >> 2, t = lane & 3;
+
+  const int chunk = build_plan(p, s_start, s_red);
+  const int total_items = s_start[p.batch];
+  if (blockIdx.x == 0) {
+    for (int b = tid; b < p.batch; b += kDecThreads)
+      p.binfo[b] = make_int2(s_start[b], s_start[b + 1] - s_start[b]);
+  }
+
+  const int ydim = p.num_kv_heads * p.mtiles;
+  const long long total_work = static_cast<long long>(total_items) * ydim;
+  const uint32_t ring = smem_u32(smem) + warp * S::kWarpBytes;
+  const T* kc = static_cast<const T*>(p.k_cache);
+  const T* vc = static_cast<const T*>(p.v_cache);
+  const int bs = p.block_size;
+
+  for (long long w = blockIdx.x; w < total_work; w += gridDim.x) {
+    const int item = static_cast<int>(w / ydim);
+    const int y = static_cast<int>(w - static_cast<long long>(item) * ydim);
+    const int kvh = y / p.mtiles, mt = y - kvh * p.mtiles;
+    // sequence of this item: last b with s_start[b] <= item
+    int lo = 0, hi = p.batch - 1;
+    while (lo < hi) {
+      const int mid = (lo + hi + 1) >> 1;
+      if (s_start[mid] <= item) lo = mid; else hi = mid - 1;
+    }
+    const int b = lo;
+    const int nsplit = s_start[b + 1] - s_start[b];
+    const int ctx = load_ctx(p, b);
+    const int tok_begin = (item - s_start[b]) * chunk;
+    const int tok_end = min(ctx, tok_begin + chunk);
+    const int32_t* table = p.block_tables + static_cast<int64_t>(b) * p.bt_stride;
+    const int rows_valid = min(16, p.group - mt * 16);
+    const int h0 = kvh * p.group + mt * 16;
+
+    // tiles of this warp: tokens tok_begin + (i*kDecWarps + warp)*16
+    const int span = tok_end - tok_begin;
+    const int cta_tiles = span > 0 ? (span + kTileTok - 1) / kTileTok : 0;
+    const int my_tiles = cta_tiles > warp ? (cta_tiles - warp + kDecWarps - 1) / kDecWarps : 0;
+
+    auto issue = [&](int i) {
+      // stage i % kDecStages <- tile i of this warp (or nothing past the end)
+      if (i < my_tiles) {
+        const int stage = i % kDecStages;
+        const int tok0 = tok_begin + (i * kDecWarps + warp) * kTileTok;
+        const int blk0 = tok0 / bs, off0 = tok0 - blk0 * bs;
+        // lane r (r < 16) resolves row r; others mirror it
+        const int r_me = lane & 15;
+        int off = off0 + r_me, blk = blk0;
+        while (off >= bs) { off -= bs; ++blk; }
+        int slot = -1;
+        if (tok0 + r_me < tok_end) {
+          const int pb = __ldg(table + blk);
+          if (pb >= 0 && pb < p.num_blocks) slot = pb * bs + off;
+        }
+        const uint32_t live = __ballot_sync(0xffffffffu, slot >= 0) & 0xffffu;
+        if (lane == 0) s_mask[warp][stage] = live;
+        const uint32_t kdst = ring + stage * S::kStageBytes;
+        const uint32_t vdst = kdst + S::kTileBytes;
+        const int c = lane % CPR, r0 = lane / CPR;
+#pragma unroll
+        for (int it = 0; it < LOAD_ITERS; ++it) {
+          const int r = r0 + it * RPI;
+          const int s = __shfl_sync(0xffffffffu, slot, r);
+          const int64_t eoff = s >= 0 ? (static_cast<int64_t>(s) * p.num_kv_heads + kvh) * D + c * 8 : 0;
+          const uint32_t doff = r * S::kRowBytes + ((c ^ (r & 7)) << 4);
+          cp_async16(kdst + doff, kc + eoff, s >= 0 ? 16 : 0);
+          cp_async16(vdst + doff, vc + eoff, s >= 0 ? 16 : 0);
+        }
+      }
+      cp_async_commit();
+    };
+
+#pragma unroll
+    for (int i = 0; i < kDecStages - 1; ++i) issue(i);
+
+    // Q fragments: rows g and g+8 of the 16-row tile, zero past the group.
+    uint32_t qa[KSTEPS][4];
+    {
+      const T* qbase = static_cast<const T*>(p.q) + (static_cast<int64_t>(b) * p.num_heads + h0) * D;
+      const bool v0 = g < rows_valid, v1 = g + 8 < rows_valid;
+      const uint32_t* q0 = reinterpret_cast<const uint32_t*>(qbase + static_cast<int64_t>(g) * D);
+      const uint32_t* q1 = reinterpret_cast<const uint32_t*>(qbase + static_cast<int64_t>(g + 8) * D);
+#pragma unroll
+      for (int ks = 0; ks < KSTEPS; ++ks) {
+        qa[ks][0] = v0 ? __ldg(q0 + ks * 8 + t) : 0u;
+        qa[ks][1] = v1 ? __ldg(q1 + ks * 8 + t) : 0u;
+        qa[ks][2] = v0 ? __ldg(q0 + ks * 8 + 4 + t) : 0u;
+        qa[ks][3] = v1 ? __ldg(q1 + ks * 8 + 4 + t) : 0u;
+      }
+    }
+
+    float o[NT][4];
+#pragma unroll
+    for (int j = 0; j < NT; ++j) { o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.f; }
+    float m0 = kNegBig, m1 = kNegBig, l0 = 0.f, l1 = 0.f;
+
+    for (int i = 0; i < my_tiles; ++i) {
+      cp_async_wait<kDecStages - 2>();
+      __syncwarp();
+      const int stage = i % kDecStages;
+      const uint32_t kbase = ring + stage * S::kStageBytes;
+      const uint32_t vbase = kbase + S::kTileBytes;
+      const uint32_t live = s_mask[warp][stage];
+
+      float s[2][4];
+#pragma unroll
+      for (int n = 0; n < 2; ++n) { s[n][0] = s[n][1] = s[n][2] = s[n][3] = 0.f; }
+      {
+        const int row = (lane & 7) + ((lane >> 4) << 3);
+        const int csel = (lane >> 3) & 1;
+#pragma unroll
+        for (int ks = 0; ks < KSTEPS; ++ks) {
+          uint32_t kb[4];
+          ldmatrix_x4(kb, kbase + row * S::kRowBytes + (((2 * ks + csel) ^ (row & 7)) << 4));
+          Mma16816<T>::run(s[0], qa[ks], kb[0], kb[1]);
+          Mma16816<T>::run(s[1], qa[ks], kb[2], kb[3]);
+        }
+      }
+      // Issue the next tile now: its slot was released at the end of the
+      // previous iteration, and the loads overlap the softmax below.
+      issue(i + kDecStages - 1);
+
+      float mx0 = kNegBig, mx1 = kNegBig;
+#pragma unroll
+      for (int n = 0; n < 2; ++n) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int col = n * 8 + 2 * t + (e & 1);
+          const bool ok = (live >> col) & 1u;
+          s[n][e] = ok ? s[n][e] * p.scale_log2 : -INFINITY;
+        }
+        mx0 = fmaxf(mx0, fmaxf(s[n][0], s[n][1]));
+        mx1 = fmaxf(mx1, fmaxf(s[n][2], s[n][3]));
+      }
+      mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));
+      mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
+      mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
+      mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
+      const float mn0 = fmaxf(m0, mx0), mn1 = fmaxf(m1, mx1);
+      const float a0 = exp2f(m0 - mn0), a1 = exp2f(m1 - mn1);
+      m0 = mn0; m1 = mn1;
+      float ps0 = 0.f, ps1 = 0.f;
+#pragma unroll
+      for (int n = 0; n < 2; ++n) {
+        s[n][0] = exp2f(s[n][0] - mn0); s[n][1] = exp2f(s[n][1] - mn0);
+        s[n][2] = exp2f(s[n][2] - mn1); s[n][3] = exp2f(s[n][3] - mn1);
+        ps0 += s[n][0] + s[n][1];
+        ps1 += s[n][2] + s[n][3];
+      }
+      l0 = l0 * a0 + ps0;  // per-thread partial sums; the quad is reduced at the end
+      l1 = l1 * a1 + ps1;
+      uint32_t pa[4];
+      pa[0] = pack2<T>(s[0][0], s[0][1]);
+      pa[1] = pack2<T>(s[0][2], s[0][3]);
+      pa[2] = pack2<T>(s[1][0], s[1][1]);
+      pa[3] = pack2<T>(s[1][2], s[1][3]);
+      {
+        const int row = (lane & 7) + (((lane >> 3) & 1) << 3);
+        const int csel = lane >> 4;
+#pragma unroll
+        for (int jp = 0; jp < KSTEPS; ++jp) {
+          uint32_t vb[4];
+          ldmatrix_x4_trans(vb, vbase + row * S::kRowBytes + (((2 * jp + csel) ^ (row & 7)) << 4));
+          float* oa = o[2 * jp];
+          float* ob = o[2 * jp + 1];
+          oa[0] *= a0; oa[1] *= a0; oa[2] *= a1; oa[3] *= a1;
+          ob[0] *= a0; ob[1] *= a0; ob[2] *= a1; ob[3] *= a1;
+          Mma16816<T>::run(o[2 * jp], pa, vb[0], vb[1]);
+          Mma16816<T>::run(o[2 * jp + 1], pa, vb[2], vb[3]);
+        }
+      }
+      __syncwarp();  // all lanes are done with this stage before it is refilled
+    }
+    cp_async_wait<0>();
+
+    l0 += __shfl_xor_sync(0xffffffffu, l0, 1);
+    l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
+    l1 += __shfl_xor_sync(0xffffffffu, l1, 1);
+    l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
+
+    // ---- merge the four warps through shared memory (the ring is idle now) ----
+    __syncthreads();
+    float* sO = reinterpret_cast<float*>(smem);
+    float* sML = sO + kDecWarps * 16 * S::kMergeStride;
+    {
+      float* mine = sO + warp * 16 * S::kMergeStride;
+#pragma unroll
+      for (int j = 0; j < NT; ++j) {
+        *reinterpret_cast<float2*>(mine + g * S::kMergeStride + j * 8 + 2 * t) = make_float2(o[j][0], o[j][1]);
+        *reinterpret_cast<float2*>(mine + (g + 8) * S::kMergeStride + j * 8 + 2 * t) = make_float2(o[j][2], o[j][3]);
+      }
+      if (t == 0) {
+        sML[(warp * 16 + g) * 2] = m0;
+        sML[(warp * 16 + g) * 2 + 1] = l0;
+        sML[(warp * 16 + g + 8) * 2] = m1;
+        sML[(warp * 16 + g + 8) * 2 + 1] = l1;
+      }
+    }
+    __syncthreads();
+    for (int idx = tid; idx < rows_valid * D; idx += kDecThreads) {
+      const int row = idx / D, d = idx - row * D;
+      float M = kNegBig;
+#pragma unroll
+      for (int ww = 0; ww < kDecWarps; ++ww) M = fmaxf(M, sML[(ww * 16 + row) * 2]);
+      float acc = 0.f, L = 0.f;
+#pragma unroll
+      for (int ww = 0; ww < kDecWarps; ++ww) {
+        const float wgt = exp2f(sML[(ww * 16 + row) * 2] - M);
+        acc += wgt * sO[(ww * 16 + row) * S::kMergeStride + d];
+        L += wgt * sML[(ww * 16 + row) * 2 + 1];
+      }
+      const int h = h0 + row;
+      if (nsplit == 1) {
+        const float r = L > 0.f ? acc / L : 0.f;
+        static_cast<T*>(p.out)[(static_cast<int64_t>(b) * p.num_heads + h) * D + d] = Elem<T>::from_f(r);
+      } else {
+        const int64_t pi = static_cast<int64_t>(item) * p.num_heads + h;
+        p.part_o[pi * D + d] = acc;
+        if (d == 0) { p.part_ml[pi * 2] = M; p.part_ml[pi * 2 + 1] = L; }
+      }
+    }
+    __syncthreads();  // the ring is handed back to the pipelines
+  }
+}
+
+// Reduces the partial results of sequences that were split, in item order.
+template <typename T, int D>
+__global__ void __launch_bounds__(128)
+paged_decode_combine_kernel(const DecodeParams p) {
+  const int b = blockIdx.x, kvh = blockIdx.y;
+  const int2 info = p.binfo[b];
+  if (info.y <= 1) return;
+  const int h_begin = kvh * p.group;
+  for (int idx = threadIdx.x; idx < p.group * D; idx += blockDim.x) {
+    const int h = h_begin + idx / D, d = idx % D;
+    float M = kNegBig;
+    for (int s = 0; s < info.y; ++s)
+      M = fmaxf(M, p.part_ml[(static_cast<int64_t>(info.x + s) * p.num_heads + h) * 2]);
+    float acc = 0.f, L = 0.f;
+    for (int s = 0; s < info.y; ++s) {
+      const int64_t pi = static_cast<int64_t>(info.x + s) * p.num_heads + h;
+      const float wgt = exp2f(p.part_ml[pi * 2] - M);
+      acc += wgt * p.part_o[pi * D + d];
+      L += wgt * p.part_ml[pi * 2 + 1];
+    }
+    const float r = L > 0.f ? acc / L : 0.f;
+    static_cast<T*>(p.out)[(static_cast<int64_t>(b) * p.num_heads + h) * D + d] = Elem<T>::from_f(r);
+  }
+}
+
+struct DecodeLayout {
+  int64_t binfo_off, ml_off, o_off, total;
+};
+static DecodeLayout decode_layout(int batch, int num_heads, int num_kv_heads, int head_dim, int max_blocks,
+                                  int block_size) {
+  const int mtiles = (num_heads / num_kv_heads + 15) / 16;
+  const int64_t items = decode_items_max(batch, num_kv_heads, mtiles, max_blocks, block_size);
+  DecodeLayout L;
+  L.binfo_off = 0;
+  L.ml_off = ((static_cast<int64_t>(batch) * 8 + 255) / 256) * 256;
+  L.o_off = L.ml_off + ((items * num_heads * 2 * 4 + 255) / 256) * 256;
+  L.total = L.o_off + items * num_heads * head_dim * 4;
+  return L;
+}
+
+template <typename T, int D>
+static int launch_decode(const DecodeParams& p, cudaStream_t st) {
+  using S = DecodeSmem<T, D>;
+  const size_t smem = S::kRingBytes + static_cast<size_t>(p.batch + 1) * sizeof(int);
+  if (smem > 227 * 1024) return fail(MV_ERR_LIMIT, "paged_decode: batch %d needs %zu bytes of shared memory", p.batch, smem);
+  static bool attr_done[64] = {};  // per kernel instantiation and per device
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= 64 || !attr_done[dev]) {
+    cudaFuncSetAttribute(paged_decode_kernel<T, D>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+    if (dev >= 0 && dev < 64) attr_done[dev] = true;
+  }
+  const int64_t items_max = decode_items_max(p.batch, p.num_kv_heads, p.mtiles, p.max_blocks, p.block_size);
+  int64_t grid = items_max * p.num_kv_heads * p.mtiles;
+  const int64_t resident = static_cast<int64_t>(kNumSMs) * kDecCtasPerSM;
+  if (grid > resident) grid = resident;
+  paged_decode_kernel<T, D><<<static_cast<int>(grid), kDecThreads, smem, st>>>(p);
+  int rc = check_launch("paged_decode_kernel");
+  if (rc) return rc;
+  paged_decode_combine_kernel<T, D><<<dim3(p.batch, p.num_kv_heads), 128, 0, st>>>(p);
+  return check_launch("paged_decode_combine_kernel");
+}
+
+}  // namespace mv
+
+extern "C" int64_t mv_paged_decode_workspace_bytes(int batch, int num_heads, int num_kv_heads, int head_dim,
+                                                   int max_blocks, int block_size) {
+  if (batch <= 0 || num_heads <= 0 || num_kv_heads <= 0 || head_dim <= 0 || max_blocks < 0 || block_size <= 0 ||
+      num_heads % num_kv_heads != 0)
+    return -1;
+  return mv::decode_layout(batch, num_heads, num_kv_heads, head_dim, max_blocks, block_size).total;
+}
+
+extern "C" int mv_paged_decode(void* out, const void* q, const void* k_cache, const void* v_cache,
+                               const void* k_scale, const void* v_scale, const int32_t* block_tables,
+                               int64_t bt_stride, int max_blocks, const void* context_lens, int ctx_is_i64, int batch,
+                               int num_heads, int num_kv_heads, int head_dim, int block_size, int64_t num_blocks,
+                               float scale, void* workspace, int64_t workspace_bytes, int dtype, void* stream) {
+  using namespace mv;
+  if (dtype != MV_F16 && dtype != MV_BF16) return fail(MV_ERR_DTYPE, "paged_decode: dtype %d", dtype);
+  if (batch < 0 || num_heads <= 0 || num_kv_heads <= 0 || block_size <= 0 || max_blocks < 0 || num_blocks < 0)
+    return fail(MV_ERR_SHAPE, "paged_decode: negative or zero size");
+  if (num_heads % num_kv_heads != 0)
+    return fail(MV_ERR_SHAPE, "paged_decode: num_heads %d is not a multiple of num_kv_heads %d", num_heads, num_kv_heads);
+  if (head_dim != 64 && head_dim != 128) return fail(MV_ERR_SHAPE, "paged_decode: head_dim %d not in {64,128}", head_dim);
+  if (batch == 0) return MV_OK;
+  if (!out || !q || !k_cache || !v_cache || !block_tables || !context_lens || !workspace)
+    return fail(MV_ERR_NULL, "paged_decode: null pointer");
+  if (k_scale || v_scale) return fail(MV_ERR_DTYPE, "paged_decode: int8 cache is not built yet");
+  if (!aligned16(out) || !aligned16(q) || !aligned16(k_cache) || !aligned16(v_cache) || !aligned16(workspace))
+    return fail(MV_ERR_ALIGN, "paged_decode: pointers must be 16-byte aligned");
+  if (bt_stride < max_blocks) return fail(MV_ERR_SHAPE, "paged_decode: block table stride smaller than its width");
+  if (num_blocks * block_size > 0x7fffffffLL) return fail(MV_ERR_LIMIT, "paged_decode: more than 2^31 cache slots");
+  const DecodeLayout L = decode_layout(batch, num_heads, num_kv_heads, head_dim, max_blocks, block_size);
+  if (workspace_bytes < L.total)
+    return fail(MV_ERR_WORKSPACE, "paged_decode: workspace %lld < %lld bytes", (long long)workspace_bytes, (long long)L.total);
+
+  DecodeParams p;
+  p.out = out; p.q = q; p.k_cache = k_cache; p.v_cache = v_cache;
+  p.block_tables = block_tables; p.bt_stride = bt_stride; p.max_blocks = max_blocks;
+  p.context_lens = context_lens; p.ctx_is_i64 = ctx_is_i64;
+  p.batch = batch; p.num_heads = num_heads; p.num_kv_heads = num_kv_heads;
+  p.group = num_heads / num_kv_heads; p.mtiles = (p.group + 15) / 16;
+  p.block_size = block_size; p.num_blocks = num_blocks;
+  p.scale_log2 = scale * 1.4426950408889634f;
+  p.target_items = decode_target_items(num_kv_heads, p.mtiles);
+  unsigned char* ws = static_cast<unsigned char*>(workspace);
+  p.binfo = reinterpret_cast<int2*>(ws + L.binfo_off);
+  p.part_ml = reinterpret_cast<float*>(ws + L.ml_off);
+  p.part_o = reinterpret_cast<float*>(ws + L.o_off);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (dtype == MV_F16) return head_dim == 128 ? launch_decode<__half, 128>(p, st) : launch_decode<__half, 64>(p, st);
+  return head_dim == 128 ? launch_decode<__nv_bfloat16, 128>(p, st) : launch_decode<__nv_bfloat16, 64>(p, st);
+}

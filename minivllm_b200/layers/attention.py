@@ -1,0 +1,135 @@
+"""Attention operators of the engine, routed through the C-ABI library into
+hand-written sm_100a CUDA.
+
+Same names and positional arguments as src/myvllm/layers/attention.py of the
+reference (`store_kvcache` :67, `flash_attention_prefill` :212,
+`paged_attention_decode` :418, `Attention` :476), so the reference's call
+sites (src/myvllm/models/qwen3.py:110) work unchanged.  There is no Triton, no
+PyTorch and no CPU path behind these functions: a missing library raises.
+
+Differences from the reference, all deliberate:
+  * no `.contiguous()` copies: token strides are passed to the kernels, so the
+    non-contiguous `v` split view of a fused qkv projection is read in place;
+  * the block size used to address the cache is the cache's own second
+    dimension; the `block_size` argument is only checked against it (the
+    reference module defaults it to 16 while the engine allocates 256-token
+    blocks, which corrupts decode);
+  * optional int8 caches (`k_scale` / `v_scale` keyword arguments).
+"""
+import torch
+import torch.nn as nn
+
+from .. import _cabi
+from ..utils.context import get_context
+
+_workspaces = {}
+
+
+def _decode_workspace(device, nbytes):
+    """Grow-only scratch per device for the split-K partial results."""
+    ws = _workspaces.get(device)
+    if ws is None or ws.numel() < nbytes:
+        ws = torch.empty(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
+        _workspaces[device] = ws
+    return ws
+
+
+def _row_stride(x, name):
+    """Token stride (elements) of a (tokens, heads, head_dim) tensor whose last two dims are dense."""
+    t, h, d = x.shape
+    if x.stride(2) != 1 or (h > 1 and x.stride(1) != d):
+        raise ValueError(f"{name}: heads and head_dim must be contiguous within a token")
+    return x.stride(0) if t > 1 else h * d
+
+
+def store_kvcache(key, value, k_cache, v_cache, slot_mapping, block_size, k_scale=None, v_scale=None):
+    """Scatter `key`/`value` (tokens, kv_heads, head_dim) into the paged caches
+    (blocks, block_size, kv_heads, head_dim) at `slot_mapping` (int64, -1 skips).
+
+    With `k_scale`/`v_scale` (blocks, block_size, kv_heads) fp16 tensors the
+    caches are int8 and rows are quantised per token and head on the way in.
+    Reference: src/myvllm/layers/attention.py:67-108.
+    """
+    _cabi.require_cuda(key, value, k_cache, v_cache, slot_mapping)
+    num_tokens, num_kv_heads, head_dim = key.shape
+    assert value.shape == key.shape, "K and V shapes must match"
+    assert k_cache.shape == v_cache.shape, "K and V cache shapes must match"
+    assert slot_mapping.numel() == num_tokens, "Slot mapping size must match number of tokens"
+    if k_cache.dim() != 4 or k_cache.shape[2] != num_kv_heads or k_cache.shape[3] != head_dim:
+        raise ValueError(f"cache shape {tuple(k_cache.shape)} does not match kv_heads={num_kv_heads}, head_dim={head_dim}")
+    if block_size != k_cache.shape[1]:
+        raise ValueError(f"block_size {block_size} differs from the cache's block dimension {k_cache.shape[1]}")
+    if not (k_cache.is_contiguous() and v_cache.is_contiguous()):
+        raise ValueError("caches must be contiguous")
+    if slot_mapping.dtype != torch.int64 or not slot_mapping.is_contiguous():
+        raise ValueError("slot_mapping must be a contiguous int64 tensor")
+    if value.dtype != key.dtype:
+        raise ValueError("key and value dtypes differ")
+    quant = k_scale is not None or v_scale is not None
+    if quant:
+        if k_scale is None or v_scale is None:
+            raise ValueError("k_scale and v_scale must be given together")
+        if k_cache.dtype != torch.int8 or v_cache.dtype != torch.int8:
+            raise ValueError("int8 caches are required when scales are given")
+        for s in (k_scale, v_scale):
+            if s.dtype != torch.float16 or tuple(s.shape) != tuple(k_cache.shape[:3]) or not s.is_contiguous():
+                raise ValueError("scales must be contiguous fp16 tensors of shape (blocks, block_size, kv_heads)")
+    elif k_cache.dtype != key.dtype:
+        raise ValueError(f"cache dtype {k_cache.dtype} differs from key dtype {key.dtype}")
+    num_slots = k_cache.shape[0] * k_cache.shape[1]
+    rc = _cabi.lib().mv_store_kvcache(
+        key.data_ptr(), value.data_ptr(), _row_stride(key, "key"), _row_stride(value, "value"),
+        k_cache.data_ptr(), v_cache.data_ptr(),
+        k_scale.data_ptr() if quant else None, v_scale.data_ptr() if quant else None,
+        slot_mapping.data_ptr(), num_tokens, num_slots, num_kv_heads, head_dim,
+        _cabi.dtype_code(key.dtype), _cabi.stream_ptr())
+    _cabi.check(rc)
+
+
+def paged_attention_decode(query, k_cache, v_cache, block_tables, context_lens, scale, num_heads, num_kv_heads,
+                           head_dim, block_size, k_scale=None, v_scale=None, workspace=None):
+    """Decode attention of one new token per sequence over the paged cache.
+
+    query (batch, heads, head_dim); block_tables (batch, max_blocks) int32,
+    negative entries carry no tokens; context_lens (batch,) int32 or int64.
+    Returns a new (batch, heads, head_dim) tensor in query's dtype.
+    Reference: src/myvllm/layers/attention.py:418-473.
+    """
+    _cabi.require_cuda(query, k_cache, v_cache, block_tables, context_lens)
+    batch = query.shape[0]
+    if tuple(query.shape) != (batch, num_heads, head_dim):
+        raise ValueError(f"query shape {tuple(query.shape)} is not (batch, {num_heads}, {head_dim})")
+    if k_cache.dim() != 4 or k_cache.shape != v_cache.shape or k_cache.shape[2] != num_kv_heads or \
+            k_cache.shape[3] != head_dim:
+        raise ValueError(f"cache shape {tuple(k_cache.shape)} does not match kv_heads={num_kv_heads}, head_dim={head_dim}")
+    if block_size != k_cache.shape[1]:
+        raise ValueError(f"block_size {block_size} differs from the cache's block dimension {k_cache.shape[1]}")
+    if block_tables.dtype != torch.int32 or block_tables.dim() != 2 or block_tables.shape[0] != batch or \
+            block_tables.stride(1) != 1:
+        raise ValueError("block_tables must be a (batch, max_blocks) int32 tensor with dense rows")
+    if context_lens.dtype not in (torch.int32, torch.int64) or context_lens.numel() != batch or \
+            not context_lens.is_contiguous():
+        raise ValueError("context_lens must be a contiguous (batch,) int32 or int64 tensor")
+    if not query.is_contiguous():
+        query = query.contiguous()
+    out = torch.empty_like(query)
+    if batch == 0:
+        return out
+    max_blocks = block_tables.shape[1]
+    L = _cabi.lib()
+    need = L.mv_paged_decode_workspace_bytes(batch, num_heads, num_kv_heads, head_dim, max_blocks, block_size)
+    if need < 0:
+        raise ValueError("paged_attention_decode: invalid shape")
+    if workspace is None:
+        workspace = _decode_workspace(query.device, need)
+    quant = k_scale is not None
+    rc = L.mv_paged_decode(
+        out.data_ptr(), query.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(),
+        k_scale.data_ptr() if quant else None, v_scale.data_ptr() if quant else None,
+        block_tables.data_ptr(), block_tables.stride(0) if batch > 1 else max_blocks, max_blocks,
+        context_lens.data_ptr(), 1 if context_lens.dtype == torch.int64 else 0,
+        batch, num_heads, num_kv_heads, head_dim, block_size, k_cache.shape[0], float(scale),
+        workspace.data_ptr(), workspace.numel() * workspace.element_size(),
+        _cabi.dtype_code(query.dtype), _cabi.stream_ptr())
+    _cabi.check(rc)
+    return out

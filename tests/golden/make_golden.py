@@ -1,0 +1,100 @@
+"""Generates tests/golden/*.npz by running the REFERENCE's own code on the CPU.
+
+Run once, in a container that has the reference checkout (default
+/root/reference, or $MINIVLLM_REFERENCE):
+
+    python tests/golden/make_golden.py
+
+What is recorded (inputs are regenerated from seeds by the tests; only the
+reference's outputs are stored, as fp32):
+  * decode_*.npz   : benchmark_decoding.py `decode_torch_optimized` and
+                     `naive_decode_attention`, and the Triton kernel
+                     `paged_attention_decode` under TRITON_INTERPRET=1;
+  * prefill_*.npz  : benchmark_prefilling.py `pytorch_standard_attention` and
+                     the Triton kernel `flash_attention_prefill` (interpreter);
+  * store_*.npz    : the Triton kernel `store_kvcache` (interpreter).
+The fixtures are small so that the interpreter finishes in seconds and the
+files stay a few hundred KB.
+"""
+import os
+import sys
+
+os.environ["TRITON_INTERPRET"] = "1"
+os.environ.setdefault("TORCHDYNAMO_DISABLE", "1")
+
+import numpy as np
+import torch
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+ROOT = os.path.dirname(os.path.dirname(HERE))
+REF = os.environ.get("MINIVLLM_REFERENCE", "/root/reference")
+sys.path.insert(0, ROOT)
+sys.path.insert(0, REF)
+sys.path.insert(0, os.path.join(REF, "src"))
+
+from minivllm_b200 import synth  # noqa: E402
+
+# Cases: name -> generator kwargs.  Rounded to fp16/bf16 first, then fed to the reference in fp32.
+DECODE_CASES = {
+    "decode_small_bs16": dict(seed=10, batch=3, ctx_lo=5, ctx_hi=70, num_heads=4, num_kv_heads=2, head_dim=64,
+                              block_size=16),
+    "decode_gqa4_bs256": dict(seed=11, batch=4, ctx_lo=64, ctx_hi=600, num_heads=8, num_kv_heads=2, head_dim=128,
+                              block_size=256),
+    "decode_cfg0_like": dict(seed=0, batch=16, ctx_lo=64, ctx_hi=1024, num_heads=16, num_kv_heads=8, head_dim=128,
+                             block_size=256),
+}
+PREFILL_CASES = {
+    "prefill_small": dict(seed=20, num_seqs=3, len_lo=1, len_hi=70, num_heads=4, num_kv_heads=2, head_dim=64),
+    "prefill_gqa4": dict(seed=21, num_seqs=3, len_lo=40, len_hi=200, num_heads=8, num_kv_heads=2, head_dim=128),
+}
+STORE_CASES = {
+    "store_small": dict(seed=30, num_tokens=40, num_blocks=8, block_size=16, num_kv_heads=2, head_dim=64,
+                        pad_frac=0.2),
+}
+TRITON_MAX_TOKENS = 3000  # interpreter budget
+
+
+def rounded(x, dtype):
+    return x.to(dtype).to(torch.float32)
+
+
+def main():
+    import benchmark_decoding as bd
+    import benchmark_prefilling as bp
+    from myvllm.layers import attention as ref_attn
+
+    for name, kw in DECODE_CASES.items():
+        d = synth.decode_inputs(**kw)
+        q, kc, vc = (rounded(d[k], torch.float16) for k in ("q", "k_cache", "v_cache"))
+        args = (q, kc, vc, d["block_tables"], d["context_lens"], d["scale"], d["num_heads"], d["num_kv_heads"],
+                d["head_dim"], d["block_size"])
+        out = {"torch_optimized": bd.decode_torch_optimized(*args).numpy(),
+               "naive": bd.naive_decode_attention(*args).numpy()}
+        if int(d["context_lens"].sum()) <= TRITON_MAX_TOKENS:
+            out["triton"] = ref_attn.paged_attention_decode(*args).numpy()
+        np.savez_compressed(os.path.join(HERE, name + ".npz"), kwargs=repr(kw), **out)
+        print(name, {k: v.shape for k, v in out.items()})
+
+    for name, kw in PREFILL_CASES.items():
+        d = synth.prefill_inputs(**kw)
+        q, k, v = (rounded(d[x], torch.bfloat16) for x in ("q", "k", "v"))
+        args = (q, k, v, d["cu_seqlens"], d["scale"], d["num_heads"], d["num_kv_heads"], d["head_dim"])
+        out = {"torch_standard": bp.pytorch_standard_attention(*args).numpy()}
+        if q.shape[0] <= TRITON_MAX_TOKENS:
+            out["triton"] = ref_attn.flash_attention_prefill(*args).numpy()
+        np.savez_compressed(os.path.join(HERE, name + ".npz"), kwargs=repr(kw), **out)
+        print(name, {k: v.shape for k, v in out.items()})
+
+    for name, kw in STORE_CASES.items():
+        d = synth.store_inputs(**kw)
+        k, v = rounded(d["k"], torch.bfloat16), rounded(d["v"], torch.bfloat16)
+        shape = (d["num_blocks"], d["block_size"], d["num_kv_heads"], d["head_dim"])
+        kc = torch.full(shape, -7.0)
+        vc = torch.full(shape, -7.0)
+        ref_attn.store_kvcache(k, v, kc, vc, d["slot_mapping"], d["block_size"])
+        np.savez_compressed(os.path.join(HERE, name + ".npz"), kwargs=repr(kw), k_cache=kc.numpy(), v_cache=vc.numpy())
+        print(name, kc.shape)
+
+
+if __name__ == "__main__":
+    main()
