@@ -27,6 +27,9 @@ sys.path.insert(0, ROOT)
 from minivllm_b200 import synth  # noqa: E402
 
 L2_BYTES = 126 * 1024 * 1024
+# dram__bytes_read+write / algorithmic bytes of paged_decode_kernel, from the ncu capture summarised in
+# profiles/paged_decode_fp16_b64_ctx1024-4096.md (traffic grows in proportion to the KV tokens read)
+NCU_TRAFFIC_RATIO = 652.4 / 652.1
 
 
 def peaks():
@@ -38,41 +41,62 @@ def peaks():
 
 
 class ClockSampler:
-    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
-    Q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
-         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+    """Samples SM clocks and throttle reasons through NVML (read-only) while the timed region runs."""
 
-    def __init__(self, index):
-        self.index, self.rows, self.proc = index, [], None
+    def __init__(self, index, period_s=0.005):
+        self.index, self.period, self.rows, self.stop = index, period_s, [], threading.Event()
+        self.thread = None
 
     def __enter__(self):
         try:
-            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
-                                          "-i", str(self.index), "-lms", "100"], stdout=subprocess.PIPE,
-                                         stderr=subprocess.DEVNULL, text=True)
-            self.thread = threading.Thread(target=self._read, daemon=True)
+            import pynvml
+            pynvml.nvmlInit()
+            self.nv = pynvml
+            self.h = pynvml.nvmlDeviceGetHandleByIndex(self._physical_index())
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM)
+            self.thread = threading.Thread(target=self._loop, daemon=True)
             self.thread.start()
-        except OSError:
-            self.proc = None
+        except Exception:  # no NVML: the summary says "unsampled"
+            self.thread = None
         return self
 
-    def _read(self):
-        for line in self.proc.stdout:
-            self.rows.append([c.strip() for c in line.split(",")])
+    def _physical_index(self):
+        vis = os.environ.get("CUDA_VISIBLE_DEVICES")
+        if vis:
+            ids = [v for v in vis.split(",") if v.strip() != ""]
+            if self.index < len(ids) and ids[self.index].strip().isdigit():
+                return int(ids[self.index])
+        return self.index
+
+    def _loop(self):
+        nv = self.nv
+        while not self.stop.is_set():
+            try:
+                self.rows.append((nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM),
+                                  nv.nvmlDeviceGetCurrentClocksEventReasons(self.h)))
+            except Exception:
+                break
+            time.sleep(self.period)
 
     def __exit__(self, *a):
-        if self.proc:
-            self.proc.terminate()
+        self.stop.set()
+        if self.thread:
             self.thread.join(timeout=2)
 
     def summary(self):
-        sm = sorted(int(r[0]) for r in self.rows if r and r[0].isdigit())
-        if not sm:
+        if not self.rows:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["unsampled"]}
-        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        reasons = [n for i, n in enumerate(names) if any(len(r) > 2 + i and r[2 + i] == "Active" for r in self.rows)]
-        mx = max(int(r[1]) for r in self.rows if len(r) > 1 and r[1].isdigit())
-        return {"sm_mhz": sm[len(sm) // 2], "sm_max_mhz": mx, "reasons": reasons, "samples": len(sm)}
+        nv = self.nv
+        sm = sorted(r[0] for r in self.rows)
+        bits = 0
+        for r in self.rows:
+            bits |= r[1]
+        names = {"hw_slowdown": nv.nvmlClocksEventReasonHwSlowdown,
+                 "hw_thermal_slowdown": nv.nvmlClocksEventReasonHwThermalSlowdown,
+                 "sw_thermal_slowdown": nv.nvmlClocksEventReasonSwThermalSlowdown,
+                 "sw_power_cap": nv.nvmlClocksEventReasonSwPowerCap}
+        reasons = [k for k, v in names.items() if bits & v]
+        return {"sm_mhz": sm[len(sm) // 2], "sm_max_mhz": self.max_mhz, "reasons": reasons, "samples": len(sm)}
 
 
 # ----------------------------------------------------------------------------
@@ -208,6 +232,62 @@ def device_timed(fn, steps, warmup, dist_on):
     return total_ms, per_call_ms
 
 
+def _time_calls(fns, iters, warmup=5):
+    """Average device time (ms) of calls taken round-robin from `fns` (distinct inputs defeat L2 reuse)."""
+    for i in range(warmup):
+        fns[i % len(fns)]()
+    torch.cuda.synchronize()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for i in range(iters):
+        fns[i % len(fns)]()
+    b.record()
+    torch.cuda.synchronize()
+    return a.elapsed_time(b) / iters
+
+
+def extras(device, pk):
+    """Secondary numbers of the same run: the exact small decode configuration and store_kvcache."""
+    from minivllm_b200.layers import attention as A
+    out = {}
+    # decode, exact configuration: batch 16, ctx [64,1024] (34 MB of KV, fits L2) -> rotate 8 cache copies
+    d = synth.decode_inputs(seed=0)
+    dt = torch.float16
+    q, bt, cl = d["q"].to(dt).to(device), d["block_tables"].to(device), d["context_lens"].to(device)
+    copies = [(d["k_cache"].to(dt).to(device).clone(), d["v_cache"].to(dt).to(device).clone()) for _ in range(8)]
+    fns = [lambda kc=kc, vc=vc: A.paged_attention_decode(q, kc, vc, bt, cl, d["scale"], 16, 8, 128, 256)
+           for kc, vc in copies]
+    ms = _time_calls(fns, 200, 20)
+    nbytes = synth.decode_bytes(d["context_lens"], 16, 16, 8, 128, 2, bt.shape[1])
+    out["decode_batch16_ctx64_1024"] = {"us_per_call": ms * 1e3, "GBps": nbytes / ms / 1e6,
+                                        "frac_of_measured_peak": nbytes / ms / 1e6 / pk["hbm_gbs"],
+                                        "l2": "8 rotating cache copies (272 MB)", "bytes": nbytes}
+    del copies, fns
+    # store_kvcache: 65,536 tokens, 8 kv heads x 128, bf16, 4096 x 256-slot cache, ~3% padding
+    s = synth.store_inputs()
+    bf = torch.bfloat16
+    slots = s["slot_mapping"].to(device)
+    valid = int((s["slot_mapping"] >= 0).sum())
+    shape = (s["num_blocks"], s["block_size"], 8, 128)
+    kc, vc = torch.zeros(shape, dtype=bf, device=device), torch.zeros(shape, dtype=bf, device=device)
+    srcs = [(s["k"].to(bf).to(device).clone(), s["v"].to(bf).to(device).clone()) for _ in range(2)]
+    fns = [lambda k=k, v=v: A.store_kvcache(k, v, kc, vc, slots, 256) for k, v in srcs]
+    ms = _time_calls(fns, 50)
+    nbytes = valid * 8 * 128 * (2 * 2 + 2 * 2) + 65536 * 8
+    out["store_kvcache_bf16"] = {"us_per_call": ms * 1e3, "GBps": nbytes / ms / 1e6,
+                                 "frac_of_measured_peak": nbytes / ms / 1e6 / pk["hbm_gbs"], "bytes": nbytes}
+    del kc, vc
+    kq, vq = torch.zeros(shape, dtype=torch.int8, device=device), torch.zeros(shape, dtype=torch.int8, device=device)
+    ks = torch.zeros(shape[:3], dtype=torch.float16, device=device)
+    vs = torch.zeros(shape[:3], dtype=torch.float16, device=device)
+    fns = [lambda k=k, v=v: A.store_kvcache(k, v, kq, vq, slots, 256, k_scale=ks, v_scale=vs) for k, v in srcs]
+    ms = _time_calls(fns, 50)
+    nbytes = valid * 8 * (128 * (2 * 2 + 2 * 1) + 2 * 2) + 65536 * 8
+    out["store_kvcache_int8"] = {"us_per_call": ms * 1e3, "GBps": nbytes / ms / 1e6,
+                                 "frac_of_measured_peak": nbytes / ms / 1e6 / pk["hbm_gbs"], "bytes": nbytes}
+    return out
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -216,6 +296,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="decode", choices=["decode"])
     ap.add_argument("--cpu-seconds", type=float, default=10.0)
+    ap.add_argument("--small", action="store_true",
+                    help="profiling case: batch 64, ctx [1024,4096] (~1.3 GB of KV), no e2e/CPU/extra legs")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
 
@@ -256,10 +338,17 @@ def main():
     from minivllm_b200 import _cabi
     _cabi.lib()
 
-    wl = DecodeWorkload(rank, device)
+    if args.small:
+        wl = DecodeWorkload(rank, device, batch=64, ctx_lo=1024, ctx_hi=4096)
+        wl.name = wl.name.replace("batch 256, ctx uniform[1024,8192]", "batch 64, ctx uniform[1024,4096]")
+    else:
+        wl = DecodeWorkload(rank, device)
     with ClockSampler(local) as clocks:
         total_ms, call_ms = device_timed(wl.step_resident, args.steps, args.warmup, dist_on)
-    e2e_total_ms, _ = device_timed(wl.step_e2e, args.steps, args.warmup, dist_on)
+    if args.small:
+        e2e_total_ms = float("nan")
+    else:
+        e2e_total_ms, _ = device_timed(wl.step_e2e, args.steps, args.warmup, dist_on)
 
     pk = peaks()
     units = wl.units_per_step * world
@@ -276,12 +365,14 @@ def main():
                 "d2h_bytes_per_step": wl.d2h_bytes},
         "gpu_launches": wl.launches_per_step * args.steps,
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": pk["hbm_gbs"], "unit": "GB/s",
-                     "frac": achieved / pk["hbm_gbs"], "traffic": None, "peak_source": pk["src"],
+                     "frac": achieved / pk["hbm_gbs"], "traffic": wl.bytes_per_step * NCU_TRAFFIC_RATIO,
+                     "traffic_note": "ncu dram bytes of the batch-64 case scaled by KV tokens", "peak_source": pk["src"],
                      "kernel": "paged_decode_kernel (+combine)", "frac_of_nominal_8TBs": achieved / 8000.0},
         "clocks": clocks.summary(),
     }
     if rank == 0:
-        if world == 1:
+        if world == 1 and not args.small:
+            line["extra"] = extras(device, pk)
             run, nbytes, sample = wl.cpu_sample()
             v, _ = time_cpu(run, nbytes / 1e9, min_seconds=args.cpu_seconds)
             line["cpu_baseline"] = {"value": v, "unit": unit, "cores": torch.get_num_threads(), "kind": "port",

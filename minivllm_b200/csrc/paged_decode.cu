@@ -23,6 +23,7 @@
 // sizeof(elem) + q and out.
 #include "common.cuh"
 #include "mma.cuh"
+#include <type_traits>
 
 namespace mv {
 
@@ -150,6 +151,7 @@ paged_decode_kernel(const DecodeParams p) {
   constexpr int LOAD_ITERS = kTileTok / RPI;
   constexpr int KSTEPS = D / 16;
   constexpr int NT = D / 8;               // output n-tiles
+  constexpr bool kSplitP = sizeof(typename Elem<T>::T2) == 4 && !std::is_same<T, __half>::value;
 
   extern __shared__ __align__(128) unsigned char smem[];
   __shared__ long long s_red[kDecWarps];
@@ -314,6 +316,20 @@ paged_decode_kernel(const DecodeParams p) {
       pa[1] = pack2<T>(s[0][2], s[0][3]);
       pa[2] = pack2<T>(s[1][0], s[1][1]);
       pa[3] = pack2<T>(s[1][2], s[1][3]);
+      // bf16 keeps 8 significant bits: carry the rounding residue of P in a
+      // second operand so that short contexts (few, large weights) stay within
+      // tolerance.  The extra MMAs are free in an HBM-bound kernel.
+      uint32_t pl[4];
+      if constexpr (kSplitP) {
+#pragma unroll
+        for (int n = 0; n < 2; ++n) {
+#pragma unroll
+          for (int hh = 0; hh < 2; ++hh) {
+            const float2 hi = Elem<T>::to_f2(*reinterpret_cast<const typename Elem<T>::T2*>(&pa[2 * n + hh]));
+            pl[2 * n + hh] = pack2<T>(s[n][2 * hh] - hi.x, s[n][2 * hh + 1] - hi.y);
+          }
+        }
+      }
       {
         const int row = (lane & 7) + (((lane >> 3) & 1) << 3);
         const int csel = lane >> 4;
@@ -327,6 +343,10 @@ paged_decode_kernel(const DecodeParams p) {
           ob[0] *= a0; ob[1] *= a0; ob[2] *= a1; ob[3] *= a1;
           Mma16816<T>::run(o[2 * jp], pa, vb[0], vb[1]);
           Mma16816<T>::run(o[2 * jp + 1], pa, vb[2], vb[3]);
+          if constexpr (kSplitP) {
+            Mma16816<T>::run(o[2 * jp], pl, vb[0], vb[1]);
+            Mma16816<T>::run(o[2 * jp + 1], pl, vb[2], vb[3]);
+          }
         }
       }
       __syncwarp();  // all lanes are done with this stage before it is refilled
@@ -427,13 +447,21 @@ template <typename T, int D>
 static int launch_decode(const DecodeParams& p, cudaStream_t st) {
   using S = DecodeSmem<T, D>;
   const size_t smem = S::kRingBytes + static_cast<size_t>(p.batch + 1) * sizeof(int);
-  if (smem > 227 * 1024) return fail(MV_ERR_LIMIT, "paged_decode: batch %d needs %zu bytes of shared memory", p.batch, smem);
-  static bool attr_done[64] = {};  // per kernel instantiation and per device
+  // 227 KB per CTA is the sm_100 limit for static + dynamic shared memory together.
+  constexpr size_t kStaticSmem = 256;
+  if (smem + kStaticSmem > 227 * 1024)
+    return fail(MV_ERR_LIMIT, "paged_decode: batch %d needs %zu bytes of shared memory", p.batch, smem);
+  static size_t attr_bytes[64] = {};  // per kernel instantiation and per device
   int dev = 0;
   cudaGetDevice(&dev);
-  if (dev < 0 || dev >= 64 || !attr_done[dev]) {
-    cudaFuncSetAttribute(paged_decode_kernel<T, D>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
-    if (dev >= 0 && dev < 64) attr_done[dev] = true;
+  if (dev < 0 || dev >= 64 || attr_bytes[dev] < smem) {
+    const cudaError_t e = cudaFuncSetAttribute(paged_decode_kernel<T, D>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                               static_cast<int>(smem));
+    if (e != cudaSuccess) {
+      cudaGetLastError();
+      return fail(MV_ERR_CUDA, "paged_decode: cudaFuncSetAttribute(%zu): %s", smem, cudaGetErrorString(e));
+    }
+    if (dev >= 0 && dev < 64) attr_bytes[dev] = smem;
   }
   const int64_t items_max = decode_items_max(p.batch, p.num_kv_heads, p.mtiles, p.max_blocks, p.block_size);
   int64_t grid = items_max * p.num_kv_heads * p.mtiles;
