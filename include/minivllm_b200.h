@@ -103,6 +103,28 @@ int mv_paged_decode(void* out, const void* q,
                     void* workspace, int64_t workspace_bytes,
                     int dtype, void* stream);
 
+/*
+ * Varlen causal prefill attention over a packed ragged batch.
+ * Replaces: src/myvllm/layers/attention.py:212-280 `flash_attention_prefill`
+ * and its Triton kernel :111-209.  Sequence s owns rows
+ * [cu_seqlens[s], cu_seqlens[s+1]) of q/k/v; row i attends to rows <= i of
+ * its own sequence; query head h reads kv head h / (num_heads/num_kv_heads).
+ * q/out are (total_tokens, num_heads, 128), k/v (total_tokens, num_kv_heads,
+ * 128); q/k/v take a token stride in elements (heads dense within a token),
+ * out is contiguous.  fp32 accumulation on the tcgen05 tensor cores.
+ * No host synchronisation: the grid is an upper bound computed from
+ * total_tokens and num_seqs.
+ * error_word points to one zero-initialised int in device memory that the
+ * caller keeps: a kernel wait that runs out of time stores a non-zero code
+ * there (and later launches return at once until the caller clears it).
+ */
+int mv_prefill_varlen(void* out, const void* q, const void* k, const void* v,
+                      int64_t q_stride_tok, int64_t k_stride_tok,
+                      int64_t v_stride_tok, const int32_t* cu_seqlens,
+                      int num_seqs, int64_t total_tokens, int num_heads,
+                      int num_kv_heads, int head_dim, float scale,
+                      int* error_word, int dtype, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

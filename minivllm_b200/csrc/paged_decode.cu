@@ -21,114 +21,9 @@
 //     and a small combine kernel reduces them in a fixed order.
 // HBM-bound: algorithmic bytes = sum(ctx) * num_kv_heads * head_dim * 2 *
 // sizeof(elem) + q and out.
-#include "common.cuh"
-#include "mma.cuh"
-#include <type_traits>
+#include "paged_decode.cuh"
 
 namespace mv {
-
-constexpr int kDecWarps = 4;
-constexpr int kDecThreads = kDecWarps * 32;
-constexpr int kDecStages = 3;
-constexpr int kTileTok = 16;                    // tokens per warp tile
-constexpr int kCtaTok = kTileTok * kDecWarps;   // tokens per CTA step
-constexpr int kChunkMax = 2048;                 // longest KV chunk of one work item
-constexpr int kDecCtasPerSM = 2;
-constexpr int kDecWaves = 2;                    // work items aimed at per resident CTA
-constexpr float kNegBig = -1e30f;               // finite "minus infinity" for running maxima
-
-struct DecodeParams {
-  void* out;
-  const void* q;
-  const void* k_cache;
-  const void* v_cache;
-  const int32_t* block_tables;
-  int64_t bt_stride;
-  int max_blocks;
-  const void* context_lens;
-  int ctx_is_i64;
-  int batch, num_heads, num_kv_heads, group, mtiles;
-  int block_size;
-  int64_t num_blocks;
-  float scale_log2;
-  int target_items;
-  int2* binfo;      // per sequence: (first item, number of items)
-  float* part_ml;   // (item, head, 2)
-  float* part_o;    // (item, head, D)
-};
-
-// Work items aimed at per (KV head, row tile): enough to give every resident
-// CTA kDecWaves items.  Shapes only, so host and device agree.
-__host__ __device__ inline int decode_target_items(int num_kv_heads, int mtiles) {
-  const int t = (kNumSMs * kDecCtasPerSM * kDecWaves) / (num_kv_heads * mtiles);
-  return t < 1 ? 1 : t;
-}
-__host__ __device__ inline int64_t decode_items_max(int batch, int num_kv_heads, int mtiles, int max_blocks,
-                                                    int block_size) {
-  const int64_t lmax = static_cast<int64_t>(max_blocks) * block_size;
-  int64_t per_seq = (lmax + kChunkMax - 1) / kChunkMax;
-  if (per_seq < 1) per_seq = 1;
-  return decode_target_items(num_kv_heads, mtiles) + static_cast<int64_t>(batch) * per_seq;
-}
-
-__device__ __forceinline__ int load_ctx(const DecodeParams& p, int b) {
-  long long c = p.ctx_is_i64 ? static_cast<const long long*>(p.context_lens)[b]
-                             : static_cast<long long>(static_cast<const int*>(p.context_lens)[b]);
-  const long long lim = static_cast<long long>(p.max_blocks) * p.block_size;
-  c = c < 0 ? 0 : (c > lim ? lim : c);
-  return static_cast<int>(c);
-}
-
-// Every CTA builds the same plan: chunk length and s_start[b] = first item of
-// sequence b (s_start[batch] = number of items).  Returns the chunk length.
-__device__ int build_plan(const DecodeParams& p, int* s_start, long long* s_red) {
-  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  long long sum = 0;
-  for (int b = tid; b < p.batch; b += kDecThreads) sum += load_ctx(p, b);
-#pragma unroll
-  for (int off = 16; off > 0; off >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, off);
-  if (lane == 0) s_red[warp] = sum;
-  __syncthreads();
-  long long total = 0;
-#pragma unroll
-  for (int w = 0; w < kDecWarps; ++w) total += s_red[w];
-  long long chunk = (total + p.target_items - 1) / p.target_items;
-  chunk = ((chunk + kCtaTok - 1) / kCtaTok) * kCtaTok;
-  if (chunk < kCtaTok) chunk = kCtaTok;
-  if (chunk > kChunkMax) chunk = kChunkMax;
-  const int ch = static_cast<int>(chunk);
-  __syncthreads();  // s_red is reused below
-
-  int carry = 0;
-  if (tid == 0) s_start[0] = 0;
-  for (int base = 0; base < p.batch; base += kDecThreads) {
-    const int b = base + tid;
-    int n = 0;
-    if (b < p.batch) {
-      n = (load_ctx(p, b) + ch - 1) / ch;
-      if (n < 1) n = 1;  // an empty sequence still owns one item, which writes zeros
-    }
-    int incl = n;
-#pragma unroll
-    for (int off = 1; off < 32; off <<= 1) {
-      const int v = __shfl_up_sync(0xffffffffu, incl, off);
-      if (lane >= off) incl += v;
-    }
-    if (lane == 31) s_red[warp] = incl;
-    __syncthreads();
-    int wofs = 0, tot = 0;
-#pragma unroll
-    for (int w = 0; w < kDecWarps; ++w) {
-      const int v = static_cast<int>(s_red[w]);
-      if (w < warp) wofs += v;
-      tot += v;
-    }
-    if (b < p.batch) s_start[b + 1] = carry + wofs + incl;
-    carry += tot;
-    __syncthreads();
-  }
-  return ch;
-}
 
 template <typename T, int D>
 struct DecodeSmem {
@@ -179,17 +74,8 @@ paged_decode_kernel(const DecodeParams p) {
     const int item = static_cast<int>(w / ydim);
     const int y = static_cast<int>(w - static_cast<long long>(item) * ydim);
     const int kvh = y / p.mtiles, mt = y - kvh * p.mtiles;
-    // sequence of this item: last b with s_start[b] <= item
-    int lo = 0, hi = p.batch - 1;
-    while (lo < hi) {
-      const int mid = (lo + hi + 1) >> 1;
-      if (s_start[mid] <= item) lo = mid; else hi = mid - 1;
-    }
-    const int b = lo;
-    const int nsplit = s_start[b + 1] - s_start[b];
-    const int ctx = load_ctx(p, b);
-    const int tok_begin = (item - s_start[b]) * chunk;
-    const int tok_end = min(ctx, tok_begin + chunk);
+    const DecodeItem di = find_item(p, s_start, item, chunk);
+    const int b = di.b, nsplit = di.nsplit, tok_begin = di.tok_begin, tok_end = di.tok_end;
     const int32_t* table = p.block_tables + static_cast<int64_t>(b) * p.bt_stride;
     const int rows_valid = min(16, p.group - mt * 16);
     const int h0 = kvh * p.group + mt * 16;
@@ -377,28 +263,7 @@ paged_decode_kernel(const DecodeParams p) {
       }
     }
     __syncthreads();
-    for (int idx = tid; idx < rows_valid * D; idx += kDecThreads) {
-      const int row = idx / D, d = idx - row * D;
-      float M = kNegBig;
-#pragma unroll
-      for (int ww = 0; ww < kDecWarps; ++ww) M = fmaxf(M, sML[(ww * 16 + row) * 2]);
-      float acc = 0.f, L = 0.f;
-#pragma unroll
-      for (int ww = 0; ww < kDecWarps; ++ww) {
-        const float wgt = exp2f(sML[(ww * 16 + row) * 2] - M);
-        acc += wgt * sO[(ww * 16 + row) * S::kMergeStride + d];
-        L += wgt * sML[(ww * 16 + row) * 2 + 1];
-      }
-      const int h = h0 + row;
-      if (nsplit == 1) {
-        const float r = L > 0.f ? acc / L : 0.f;
-        static_cast<T*>(p.out)[(static_cast<int64_t>(b) * p.num_heads + h) * D + d] = Elem<T>::from_f(r);
-      } else {
-        const int64_t pi = static_cast<int64_t>(item) * p.num_heads + h;
-        p.part_o[pi * D + d] = acc;
-        if (d == 0) { p.part_ml[pi * 2] = M; p.part_ml[pi * 2 + 1] = L; }
-      }
-    }
+    merge_and_write<T, D>(p, sO, sML, S::kMergeStride, rows_valid, h0, b, item, nsplit);
     __syncthreads();  // the ring is handed back to the pipelines
   }
 }
@@ -463,11 +328,8 @@ static int launch_decode(const DecodeParams& p, cudaStream_t st) {
     }
     if (dev >= 0 && dev < 64) attr_bytes[dev] = smem;
   }
-  const int64_t items_max = decode_items_max(p.batch, p.num_kv_heads, p.mtiles, p.max_blocks, p.block_size);
-  int64_t grid = items_max * p.num_kv_heads * p.mtiles;
-  const int64_t resident = static_cast<int64_t>(kNumSMs) * kDecCtasPerSM;
-  if (grid > resident) grid = resident;
-  paged_decode_kernel<T, D><<<static_cast<int>(grid), kDecThreads, smem, st>>>(p);
+  const int grid = decode_grid(p);
+  paged_decode_kernel<T, D><<<grid, kDecThreads, smem, st>>>(p);
   int rc = check_launch("paged_decode_kernel");
   if (rc) return rc;
   paged_decode_combine_kernel<T, D><<<dim3(p.batch, p.num_kv_heads), 128, 0, st>>>(p);
@@ -499,7 +361,11 @@ extern "C" int mv_paged_decode(void* out, const void* q, const void* k_cache, co
   if (batch == 0) return MV_OK;
   if (!out || !q || !k_cache || !v_cache || !block_tables || !context_lens || !workspace)
     return fail(MV_ERR_NULL, "paged_decode: null pointer");
-  if (k_scale || v_scale) return fail(MV_ERR_DTYPE, "paged_decode: int8 cache is not built yet");
+  if ((k_scale == nullptr) != (v_scale == nullptr))
+    return fail(MV_ERR_NULL, "paged_decode: k_scale and v_scale must both be set or both be null");
+  if (k_scale && head_dim != 128) return fail(MV_ERR_SHAPE, "paged_decode: int8 caches need head_dim 128");
+  if (k_scale && (!aligned16(k_scale) || !aligned16(v_scale)))
+    return fail(MV_ERR_ALIGN, "paged_decode: scale pointers must be 16-byte aligned");
   if (!aligned16(out) || !aligned16(q) || !aligned16(k_cache) || !aligned16(v_cache) || !aligned16(workspace))
     return fail(MV_ERR_ALIGN, "paged_decode: pointers must be 16-byte aligned");
   if (bt_stride < max_blocks) return fail(MV_ERR_SHAPE, "paged_decode: block table stride smaller than its width");
@@ -510,6 +376,7 @@ extern "C" int mv_paged_decode(void* out, const void* q, const void* k_cache, co
 
   DecodeParams p;
   p.out = out; p.q = q; p.k_cache = k_cache; p.v_cache = v_cache;
+  p.k_scale = static_cast<const __half*>(k_scale); p.v_scale = static_cast<const __half*>(v_scale);
   p.block_tables = block_tables; p.bt_stride = bt_stride; p.max_blocks = max_blocks;
   p.context_lens = context_lens; p.ctx_is_i64 = ctx_is_i64;
   p.batch = batch; p.num_heads = num_heads; p.num_kv_heads = num_kv_heads;
@@ -522,6 +389,13 @@ extern "C" int mv_paged_decode(void* out, const void* q, const void* k_cache, co
   p.part_ml = reinterpret_cast<float*>(ws + L.ml_off);
   p.part_o = reinterpret_cast<float*>(ws + L.o_off);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (k_scale) {
+    const int rc = dtype == MV_F16 ? launch_decode_int8<__half>(p, st) : launch_decode_int8<__nv_bfloat16>(p, st);
+    if (rc) return rc;
+    if (dtype == MV_F16) paged_decode_combine_kernel<__half, 128><<<dim3(batch, num_kv_heads), 128, 0, st>>>(p);
+    else paged_decode_combine_kernel<__nv_bfloat16, 128><<<dim3(batch, num_kv_heads), 128, 0, st>>>(p);
+    return check_launch("paged_decode_combine_kernel");
+  }
   if (dtype == MV_F16) return head_dim == 128 ? launch_decode<__half, 128>(p, st) : launch_decode<__half, 64>(p, st);
   return head_dim == 128 ? launch_decode<__nv_bfloat16, 128>(p, st) : launch_decode<__nv_bfloat16, 64>(p, st);
 }

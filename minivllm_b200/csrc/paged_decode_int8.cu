@@ -1,0 +1,336 @@
+// Paged decode attention over an int8 KV cache (per-token-per-head symmetric
+// codes with fp16 scales, written by the quantising store_kvcache).
+//
+// Same plan, work items and warp-private cp.async rings as paged_decode.cu;
+// what differs is the operand path.  Codes are dequantised in registers:
+// a byte c becomes the fp16 value c exactly (byte-permute into 0x64xx =
+// 1024 + (c ^ 0x80), minus 1152), the MMAs run in fp16 with fp32 accumulation
+// whatever the model dtype (codes are integers <= 127, q is converted), and
+// the per-token scales are applied where they factor out: the K scale on the
+// score column, the V scale on the probability column.  The k index of the
+// QK^T MMAs and the n index of the PV MMAs are permuted so that every thread
+// reads its operands with 16-byte shared-memory loads.
+// HBM-bound: algorithmic bytes = sum(ctx) * num_kv_heads * (head_dim + 2) * 2.
+#include "paged_decode.cuh"
+
+namespace mv {
+
+constexpr int kQStages = 6;  // an int8 tile is a quarter of an fp16 tile: deeper ring, same bytes in flight
+constexpr int kQD = 128;
+
+struct Int8Smem {
+  static constexpr int kRowBytes = kQD;                              // one row of codes
+  static constexpr int kTileBytes = kTileTok * kRowBytes;            // K or V codes of a tile
+  static constexpr int kScaleBytes = 2 * kTileTok * 4;               // one 4-byte word per token, K then V
+  static constexpr int kStageBytes = 2 * kTileBytes + kScaleBytes;
+  static constexpr int kWarpBytes = kQStages * kStageBytes;
+  static constexpr int kRingBytes = kDecWarps * kWarpBytes;
+  static constexpr int kMergeStride = kQD + 8;
+  static constexpr int kMergeBytes = kDecWarps * 16 * kMergeStride * 4 + kDecWarps * 16 * 2 * 4;
+  static_assert(kMergeBytes <= kRingBytes, "merge buffer must fit in the ring");
+};
+
+__device__ __forceinline__ void cp_async4(uint32_t dst_smem, const void* src, int src_bytes) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;" ::"r"(dst_smem), "l"(src), "r"(src_bytes) : "memory");
+}
+__device__ __forceinline__ uint4 lds128(uint32_t addr) {
+  uint4 v;
+  asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
+  return v;
+}
+__device__ __forceinline__ uint32_t lds32(uint32_t addr) {
+  uint32_t v;
+  asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(addr));
+  return v;
+}
+__device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {
+  uint32_t r;
+  asm("prmt.b32 %0, %1, %2, %3;" : "=r"(r) : "r"(a), "r"(b), "r"(sel));
+  return r;
+}
+// Two biased bytes (c ^ 0x80) sitting in 0x64xx halves -> the two codes as fp16.
+__device__ __forceinline__ uint32_t unbias2(uint32_t h2) {
+  const __half2 k = __halves2half2(__ushort_as_half(0x6480), __ushort_as_half(0x6480));  // 1152
+  __half2 v = __hsub2(*reinterpret_cast<__half2*>(&h2), k);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+__device__ __forceinline__ float scale_of(uint32_t word, uint32_t odd) {
+  return __half2float(__ushort_as_half(static_cast<unsigned short>(odd ? (word >> 16) : (word & 0xffffu))));
+}
+
+template <typename T>
+__global__ void __launch_bounds__(kDecThreads, kDecCtasPerSM)
+paged_decode_int8_kernel(const DecodeParams p) {
+  using S = Int8Smem;
+  constexpr int D = kQD;
+  constexpr int KSTEPS = D / 16;
+  constexpr int NT = D / 8;
+  constexpr uint32_t kMagic = 0x64646464u, kBias = 0x80808080u;
+
+  extern __shared__ __align__(128) unsigned char smem[];
+  __shared__ long long s_red[kDecWarps];
+  __shared__ uint32_t s_mask[kDecWarps][kQStages];  // low 16 bits: live rows, high 16: scale index is odd
+  int* s_start = reinterpret_cast<int*>(smem + S::kRingBytes);
+
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int g = lane >> 2, t = lane & 3;
+
+  const int chunk = build_plan(p, s_start, s_red);
+  const int total_items = s_start[p.batch];
+  if (blockIdx.x == 0) {
+    for (int b = tid; b < p.batch; b += kDecThreads)
+      p.binfo[b] = make_int2(s_start[b], s_start[b + 1] - s_start[b]);
+  }
+
+  const int ydim = p.num_kv_heads * p.mtiles;
+  const long long total_work = static_cast<long long>(total_items) * ydim;
+  const uint32_t ring = smem_u32(smem) + warp * S::kWarpBytes;
+  const int8_t* kc = static_cast<const int8_t*>(p.k_cache);
+  const int8_t* vc = static_cast<const int8_t*>(p.v_cache);
+  const int bs = p.block_size;
+
+  for (long long w = blockIdx.x; w < total_work; w += gridDim.x) {
+    const int item = static_cast<int>(w / ydim);
+    const int y = static_cast<int>(w - static_cast<long long>(item) * ydim);
+    const int kvh = y / p.mtiles, mt = y - kvh * p.mtiles;
+    const DecodeItem di = find_item(p, s_start, item, chunk);
+    const int b = di.b, nsplit = di.nsplit, tok_begin = di.tok_begin, tok_end = di.tok_end;
+    const int32_t* table = p.block_tables + static_cast<int64_t>(b) * p.bt_stride;
+    const int rows_valid = min(16, p.group - mt * 16);
+    const int h0 = kvh * p.group + mt * 16;
+
+    const int span = tok_end - tok_begin;
+    const int cta_tiles = span > 0 ? (span + kTileTok - 1) / kTileTok : 0;
+    const int my_tiles = cta_tiles > warp ? (cta_tiles - warp + kDecWarps - 1) / kDecWarps : 0;
+
+    auto issue = [&](int i) {
+      if (i < my_tiles) {
+        const int stage = i % kQStages;
+        const int tok0 = tok_begin + (i * kDecWarps + warp) * kTileTok;
+        const int blk0 = tok0 / bs, off0 = tok0 - blk0 * bs;
+        const int r_me = lane & 15;  // lanes 16..31 mirror rows 0..15
+        int off = off0 + r_me, blk = blk0;
+        while (off >= bs) { off -= bs; ++blk; }
+        int slot = -1;
+        if (tok0 + r_me < tok_end) {
+          const int pb = __ldg(table + blk);
+          if (pb >= 0 && pb < p.num_blocks) slot = pb * bs + off;
+        }
+        const int64_t sidx = static_cast<int64_t>(slot) * p.num_kv_heads + kvh;  // scale index of my row
+        const uint32_t live = __ballot_sync(0xffffffffu, slot >= 0) & 0xffffu;
+        const uint32_t odd = __ballot_sync(0xffffffffu, slot >= 0 && (sidx & 1)) & 0xffffu;
+        if (lane == 0) s_mask[warp][stage] = live | (odd << 16);
+        const uint32_t kdst = ring + stage * S::kStageBytes;
+        const uint32_t vdst = kdst + S::kTileBytes;
+        const uint32_t sdst = vdst + S::kTileBytes;
+        // scales: lanes 0..15 fetch K, lanes 16..31 fetch V, one aligned 4-byte word holding the fp16
+        {
+          const __half* sp = lane < 16 ? p.k_scale : p.v_scale;
+          const bool is_odd = sidx & 1;
+          const void* src = slot >= 0 ? static_cast<const void*>(sp + (is_odd ? sidx - 1 : sidx))
+                                      : static_cast<const void*>(sp);
+          cp_async4(sdst + lane * 4, src, slot >= 0 ? (is_odd ? 4 : 2) : 0);
+        }
+        const int c = lane & 7, r0 = lane >> 3;
+#pragma unroll
+        for (int it = 0; it < 4; ++it) {
+          const int r = r0 + it * 4;
+          const int s = __shfl_sync(0xffffffffu, slot, r);
+          const int64_t boff = s >= 0 ? (static_cast<int64_t>(s) * p.num_kv_heads + kvh) * D + c * 16 : 0;
+          const uint32_t doff = r * S::kRowBytes + ((c ^ (r & 7)) << 4);
+          cp_async16(kdst + doff, kc + boff, s >= 0 ? 16 : 0);
+          cp_async16(vdst + doff, vc + boff, s >= 0 ? 16 : 0);
+        }
+      }
+      cp_async_commit();
+    };
+
+#pragma unroll
+    for (int i = 0; i < kQStages - 1; ++i) issue(i);
+
+    // Q fragments in fp16 with the permuted k index: k-step ks of thread t
+    // covers head-dim elements 32t + 4ks .. 32t + 4ks + 3.
+    uint32_t qa[KSTEPS][4];
+    {
+      const T* qbase = static_cast<const T*>(p.q) + (static_cast<int64_t>(b) * p.num_heads + h0) * D;
+#pragma unroll
+      for (int half_row = 0; half_row < 2; ++half_row) {
+        const int row = g + 8 * half_row;
+        const bool ok = row < rows_valid;
+        const uint2* src = reinterpret_cast<const uint2*>(qbase + static_cast<int64_t>(row) * D + 32 * t);
+#pragma unroll
+        for (int ks = 0; ks < KSTEPS; ++ks) {
+          uint2 raw = ok ? __ldg(src + ks) : make_uint2(0u, 0u);
+          if constexpr (!std::is_same<T, __half>::value) {
+            const float2 a = Elem<T>::to_f2(*reinterpret_cast<typename Elem<T>::T2*>(&raw.x));
+            const float2 c2 = Elem<T>::to_f2(*reinterpret_cast<typename Elem<T>::T2*>(&raw.y));
+            raw.x = pack2<__half>(a.x, a.y);
+            raw.y = pack2<__half>(c2.x, c2.y);
+          }
+          qa[ks][half_row] = raw.x;       // k = 2t, 2t+1
+          qa[ks][2 + half_row] = raw.y;   // k = 2t+8, 2t+9
+        }
+      }
+    }
+
+    float o[NT][4];
+#pragma unroll
+    for (int j = 0; j < NT; ++j) { o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.f; }
+    float m0 = kNegBig, m1 = kNegBig, l0 = 0.f, l1 = 0.f;
+
+    for (int i = 0; i < my_tiles; ++i) {
+      cp_async_wait<kQStages - 2>();
+      __syncwarp();
+      const int stage = i % kQStages;
+      const uint32_t kbase = ring + stage * S::kStageBytes;
+      const uint32_t vbase = kbase + S::kTileBytes;
+      const uint32_t sbase = vbase + S::kTileBytes;
+      const uint32_t mask = s_mask[warp][stage];
+
+      // ---- S = Q K^T on the codes ----
+      float s[2][4];
+#pragma unroll
+      for (int n = 0; n < 2; ++n) {
+        s[n][0] = s[n][1] = s[n][2] = s[n][3] = 0.f;
+        const int row = 8 * n + g;
+        const uint4 w0 = lds128(kbase + row * S::kRowBytes + (((2 * t) ^ (row & 7)) << 4));
+        const uint4 w1 = lds128(kbase + row * S::kRowBytes + (((2 * t + 1) ^ (row & 7)) << 4));
+        const uint32_t words[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+#pragma unroll
+        for (int ks = 0; ks < KSTEPS; ++ks) {
+          const uint32_t x = words[ks] ^ kBias;
+          const uint32_t b0 = unbias2(prmt(x, kMagic, 0x4140u));
+          const uint32_t b1 = unbias2(prmt(x, kMagic, 0x4342u));
+          Mma16816<__half>::run(s[n], qa[ks], b0, b1);
+        }
+      }
+      issue(i + kQStages - 1);
+
+      // ---- K scales, mask, online softmax ----
+      float mx0 = kNegBig, mx1 = kNegBig;
+#pragma unroll
+      for (int n = 0; n < 2; ++n) {
+#pragma unroll
+        for (int e2 = 0; e2 < 2; ++e2) {
+          const int col = n * 8 + 2 * t + e2;
+          const bool ok = (mask >> col) & 1u;
+          const float ks = scale_of(lds32(sbase + col * 4), (mask >> (16 + col)) & 1u) * p.scale_log2;
+          s[n][e2] = ok ? s[n][e2] * ks : -INFINITY;
+          s[n][2 + e2] = ok ? s[n][2 + e2] * ks : -INFINITY;
+        }
+        mx0 = fmaxf(mx0, fmaxf(s[n][0], s[n][1]));
+        mx1 = fmaxf(mx1, fmaxf(s[n][2], s[n][3]));
+      }
+      mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));
+      mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
+      mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
+      mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
+      const float mn0 = fmaxf(m0, mx0), mn1 = fmaxf(m1, mx1);
+      const float a0 = exp2f(m0 - mn0), a1 = exp2f(m1 - mn1);
+      m0 = mn0; m1 = mn1;
+      float ps0 = 0.f, ps1 = 0.f;
+      uint32_t pa[4];
+#pragma unroll
+      for (int n = 0; n < 2; ++n) {
+        const float p00 = exp2f(s[n][0] - mn0), p01 = exp2f(s[n][1] - mn0);
+        const float p10 = exp2f(s[n][2] - mn1), p11 = exp2f(s[n][3] - mn1);
+        ps0 += p00 + p01;
+        ps1 += p10 + p11;
+        // V scale of the two tokens of this column pair, folded into P
+        const int col = n * 8 + 2 * t;
+        const float vs0 = scale_of(lds32(sbase + (16 + col) * 4), (mask >> (16 + col)) & 1u);
+        const float vs1 = scale_of(lds32(sbase + (17 + col) * 4), (mask >> (17 + col)) & 1u);
+        const bool ok0 = (mask >> col) & 1u, ok1 = (mask >> (col + 1)) & 1u;
+        pa[2 * n] = pack2<__half>(ok0 ? p00 * vs0 : 0.f, ok1 ? p01 * vs1 : 0.f);
+        pa[2 * n + 1] = pack2<__half>(ok0 ? p10 * vs0 : 0.f, ok1 ? p11 * vs1 : 0.f);
+      }
+      l0 = l0 * a0 + ps0;
+      l1 = l1 * a1 + ps1;
+
+      // ---- O += P V on the codes; n-tile j of thread (g, t) is head-dim element 16*col + j ----
+      {
+        const int ra = 2 * t, rb = 2 * t + 1, rc = 2 * t + 8, rd = 2 * t + 9;
+        const uint4 va = lds128(vbase + ra * S::kRowBytes + ((g ^ (ra & 7)) << 4));
+        const uint4 vb = lds128(vbase + rb * S::kRowBytes + ((g ^ (rb & 7)) << 4));
+        const uint4 vcx = lds128(vbase + rc * S::kRowBytes + ((g ^ (rc & 7)) << 4));
+        const uint4 vd = lds128(vbase + rd * S::kRowBytes + ((g ^ (rd & 7)) << 4));
+        const uint32_t wa[4] = {va.x, va.y, va.z, va.w}, wb[4] = {vb.x, vb.y, vb.z, vb.w};
+        const uint32_t wc[4] = {vcx.x, vcx.y, vcx.z, vcx.w}, wd[4] = {vd.x, vd.y, vd.z, vd.w};
+#pragma unroll
+        for (int wi = 0; wi < 4; ++wi) {
+          const uint32_t xa = wa[wi] ^ kBias, xb = wb[wi] ^ kBias, xc = wc[wi] ^ kBias, xd = wd[wi] ^ kBias;
+          const uint32_t lo01 = prmt(xa, xb, 0x5140u), lo23 = prmt(xa, xb, 0x7362u);  // tokens 2t, 2t+1
+          const uint32_t hi01 = prmt(xc, xd, 0x5140u), hi23 = prmt(xc, xd, 0x7362u);  // tokens 2t+8, 2t+9
+          const uint32_t lo[4] = {prmt(lo01, kMagic, 0x4140u), prmt(lo01, kMagic, 0x4342u),
+                                  prmt(lo23, kMagic, 0x4140u), prmt(lo23, kMagic, 0x4342u)};
+          const uint32_t hi[4] = {prmt(hi01, kMagic, 0x4140u), prmt(hi01, kMagic, 0x4342u),
+                                  prmt(hi23, kMagic, 0x4140u), prmt(hi23, kMagic, 0x4342u)};
+#pragma unroll
+          for (int jj = 0; jj < 4; ++jj) {
+            float* oj = o[4 * wi + jj];
+            oj[0] *= a0; oj[1] *= a0; oj[2] *= a1; oj[3] *= a1;
+            Mma16816<__half>::run(o[4 * wi + jj], pa, unbias2(lo[jj]), unbias2(hi[jj]));
+          }
+        }
+      }
+      __syncwarp();
+    }
+    cp_async_wait<0>();
+
+    l0 += __shfl_xor_sync(0xffffffffu, l0, 1);
+    l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
+    l1 += __shfl_xor_sync(0xffffffffu, l1, 1);
+    l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
+
+    __syncthreads();
+    float* sO = reinterpret_cast<float*>(smem);
+    float* sML = sO + kDecWarps * 16 * S::kMergeStride;
+    {
+      float* mine = sO + warp * 16 * S::kMergeStride;
+#pragma unroll
+      for (int j = 0; j < NT; ++j) {
+        // accumulator column 2t+e of n-tile j holds head-dim element 16*(2t+e) + j
+        mine[g * S::kMergeStride + 32 * t + j] = o[j][0];
+        mine[g * S::kMergeStride + 32 * t + 16 + j] = o[j][1];
+        mine[(g + 8) * S::kMergeStride + 32 * t + j] = o[j][2];
+        mine[(g + 8) * S::kMergeStride + 32 * t + 16 + j] = o[j][3];
+      }
+      if (t == 0) {
+        sML[(warp * 16 + g) * 2] = m0;
+        sML[(warp * 16 + g) * 2 + 1] = l0;
+        sML[(warp * 16 + g + 8) * 2] = m1;
+        sML[(warp * 16 + g + 8) * 2 + 1] = l1;
+      }
+    }
+    __syncthreads();
+    merge_and_write<T, D>(p, sO, sML, S::kMergeStride, rows_valid, h0, b, item, nsplit);
+    __syncthreads();
+  }
+}
+
+template <typename T>
+int launch_decode_int8(const DecodeParams& p, cudaStream_t st) {
+  const size_t smem = Int8Smem::kRingBytes + static_cast<size_t>(p.batch + 1) * sizeof(int);
+  constexpr size_t kStaticSmem = 256;
+  if (smem + kStaticSmem > 227 * 1024)
+    return fail(MV_ERR_LIMIT, "paged_decode(int8): batch %d needs %zu bytes of shared memory", p.batch, smem);
+  static size_t attr_bytes[64] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= 64 || attr_bytes[dev] < smem) {
+    const cudaError_t e = cudaFuncSetAttribute(paged_decode_int8_kernel<T>,
+                                               cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+    if (e != cudaSuccess) {
+      cudaGetLastError();
+      return fail(MV_ERR_CUDA, "paged_decode(int8): cudaFuncSetAttribute(%zu): %s", smem, cudaGetErrorString(e));
+    }
+    if (dev >= 0 && dev < 64) attr_bytes[dev] = smem;
+  }
+  paged_decode_int8_kernel<T><<<decode_grid(p), kDecThreads, smem, st>>>(p);
+  return check_launch("paged_decode_int8_kernel");
+}
+
+template int launch_decode_int8<__half>(const DecodeParams&, cudaStream_t);
+template int launch_decode_int8<__nv_bfloat16>(const DecodeParams&, cudaStream_t);
+
+}  // namespace mv

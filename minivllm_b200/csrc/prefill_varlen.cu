@@ -1,0 +1,475 @@
+// Varlen causal prefill flash attention on the Blackwell tensor cores.
+//
+// Does the work of src/myvllm/layers/attention.py:111-280 of the reference
+// (Triton, 32x32 tiles, no causal block skipping, a host sync per call).
+//
+// One CTA owns a 128-row query tile of one sequence for TWO query heads of the
+// same GQA group, so the two 128x128 problems share every K/V tile and the
+// tensor pipe always has the other head's MMAs to run while one head's
+// softmax is on the CUDA cores.  Roles (384 threads):
+//   warps 0-3   softmax of head A: thread i owns row i (= TMEM lane i)
+//   warps 4-7   softmax of head B
+//   warp  8     TMA producer: Q once, then K and V tiles through 2-stage rings
+//   warp  9     MMA issuer: one thread issues tcgen05.mma, commits to mbarriers
+// Tensor memory (512 columns): S_A | S_B | O_A | O_B, 128 fp32 columns each.
+// S = Q K^T is an SS MMA (both operands in 128B-swizzled shared memory, written
+// by TMA); the softmax warps read S with tcgen05.ld, write P (bf16/fp16, packed
+// two per column) over the first 64 columns of S with tcgen05.st, and O += P V
+// is a TS MMA (P from tensor memory, V from shared memory, MN-major).  The
+// running maximum is only moved when it grows by more than 2^8, so O in tensor
+// memory is rescaled rarely; l and the final 1/l use the same stale maximum.
+// KV tiles above the diagonal are never visited; only the diagonal tile is
+// masked.  No cluster multicast anywhere.
+//
+// Tensor-bound: FLOPs = 4 * heads * head_dim * sum_s L_s (L_s + 1) / 2.
+#include <cuda.h>
+#include "tcgen05.cuh"
+#include "mma.cuh"
+#include <type_traits>
+
+namespace mv {
+
+constexpr int kPfThreads = 384;
+constexpr int kPfTile = 128;         // query rows and KV columns per tile
+constexpr int kPfD = 128;
+constexpr int kPfHalfBytes = kPfTile * 128;                 // one 64-element half of a 128-row tile
+constexpr int kPfTileBytes = 2 * kPfHalfBytes;              // 32 KB
+constexpr int kPfStages = 2;
+constexpr int kPfSmemBytes = 2 * kPfTileBytes + 2 * kPfStages * kPfTileBytes + 1024;  // Q(2 heads) + K ring + V ring + align
+constexpr float kRescaleThreshold = 8.f;                    // log2 units
+
+struct PrefillParams {
+  void* out;
+  int64_t out_stride_tok;  // elements
+  const int32_t* cu_seqlens;
+  int num_seqs, num_heads, num_kv_heads, group, pairs;  // pairs = ceil(group / 2)
+  float scale_log2;
+  int fmt;          // 0 fp16, 1 bf16
+  int* error_word;
+};
+
+enum { BAR_Q = 0, BAR_KFULL = 1, BAR_KEMPTY = 3, BAR_VFULL = 5, BAR_VEMPTY = 7, BAR_SFULL = 9, BAR_PREADY = 11,
+       BAR_ODONE = 13, BAR_COUNT = 15 };
+
+__device__ __forceinline__ float ex2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+template <typename T>
+__global__ void __launch_bounds__(kPfThreads, 1)
+prefill_varlen_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
+                      const __grid_constant__ CUtensorMap tmap_v, const PrefillParams p) {
+  extern __shared__ unsigned char smem_raw[];
+  __shared__ __align__(8) uint64_t bars[BAR_COUNT];
+  __shared__ uint32_t s_tmem_base;
+  __shared__ int s_tile[2];       // (sequence, query tile) of this CTA, -1 = none
+  __shared__ int s_scan[16];
+  __shared__ int s_abort;
+  __shared__ int s_sticky;
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  const uint32_t q_smem = smem_base;                                  // [head 2][half 2][128][128B]
+  const uint32_t k_smem = q_smem + 2 * kPfTileBytes;                  // [stage][half][128][128B]
+  const uint32_t v_smem = k_smem + kPfStages * kPfTileBytes;
+  const uint32_t bar0 = smem_u32(bars);
+  auto bar = [&](int i) { return bar0 + 8u * i; };
+  volatile int* abort_flag = &s_abort;
+
+  // ---- which (sequence, query tile) is blockIdx.x?  tiles of a sequence in descending order ----
+  if (tid == 0) {
+    s_tile[0] = -1;
+    s_tile[1] = 0;
+    s_abort = 0;
+    s_sticky = *reinterpret_cast<volatile int*>(p.error_word);  // read once so that the whole CTA agrees
+  }
+  __syncthreads();
+  {
+    int carry = 0;
+    for (int base = 0; base < p.num_seqs; base += kPfThreads) {
+      const int s = base + tid;
+      int n = 0;
+      if (s < p.num_seqs) {
+        const int len = p.cu_seqlens[s + 1] - p.cu_seqlens[s];
+        n = len > 0 ? (len + kPfTile - 1) / kPfTile : 0;
+      }
+      int incl = n;
+#pragma unroll
+      for (int off = 1; off < 32; off <<= 1) {
+        const int v = __shfl_up_sync(0xffffffffu, incl, off);
+        if (lane >= off) incl += v;
+      }
+      if (lane == 31) s_scan[warp] = incl;
+      __syncthreads();
+      int wofs = 0, tot = 0;
+#pragma unroll
+      for (int w2 = 0; w2 < kPfThreads / 32; ++w2) {
+        const int v = s_scan[w2];
+        if (w2 < warp) wofs += v;
+        tot += v;
+      }
+      const int start = carry + wofs + incl - n;
+      const int x = static_cast<int>(blockIdx.x);
+      if (n > 0 && x >= start && x < start + n) { s_tile[0] = s; s_tile[1] = n - 1 - (x - start); }
+      carry += tot;
+      __syncthreads();
+    }
+  }
+  const int seq = s_tile[0], qtile = s_tile[1];
+  if (seq < 0) return;  // uniform: the grid is an upper bound on the number of tiles
+  // A wait that ran out anywhere (this launch or an earlier one) leaves the
+  // error word set: the remaining CTAs return at once instead of waiting too.
+  if (s_sticky != 0) return;
+
+  const int kvh = blockIdx.y / p.pairs, pair = blockIdx.y - kvh * p.pairs;
+  const int head_a = kvh * p.group + 2 * pair;
+  const bool has_b = 2 * pair + 1 < p.group;
+  const int seq_start = p.cu_seqlens[seq];
+  const int seq_len = p.cu_seqlens[seq + 1] - seq_start;
+  const int q0 = qtile * kPfTile;              // first query row of the tile within the sequence
+  const int n_kv = qtile + 1;                  // causal: KV tiles 0..qtile
+  // Rows of the first query tile have fewer than 128 keys, so the rounding of
+  // their weights to bf16 (8 significant bits) does not average out: those
+  // CTAs (the cheapest ones) also feed the rounding residue of P through a
+  // second PV MMA.  fp16 P has 11 bits and needs nothing.
+  const bool split_p = std::is_same<T, __nv_bfloat16>::value && n_kv == 1;
+
+  if (tid == 0) {
+    tc::mbar_init(bar(BAR_Q), 1);
+    for (int s = 0; s < kPfStages; ++s) {
+      tc::mbar_init(bar(BAR_KFULL + s), 1);
+      tc::mbar_init(bar(BAR_KEMPTY + s), 1);
+      tc::mbar_init(bar(BAR_VFULL + s), 1);
+      tc::mbar_init(bar(BAR_VEMPTY + s), 1);
+    }
+    for (int t = 0; t < 2; ++t) {
+      tc::mbar_init(bar(BAR_SFULL + t), 1);
+      tc::mbar_init(bar(BAR_PREADY + t), 128);
+      tc::mbar_init(bar(BAR_ODONE + t), 1);
+    }
+    tc::mbar_fence_init();
+  }
+  if (warp == 8) {
+    tc::tmem_alloc(smem_u32(&s_tmem_base), 512);
+    tc::tmem_relinquish();
+  }
+  tc::fence_before_sync();
+  __syncthreads();
+  tc::fence_after_sync();
+  const uint32_t tmem = s_tmem_base;
+
+  if (warp >= 8) {
+    if (warp == 8) {
+      // ------------------------------ TMA producer ------------------------------
+      if (lane == 0) {
+        tc::tma_prefetch_desc(&tmap_q);
+        tc::tma_prefetch_desc(&tmap_k);
+        tc::tma_prefetch_desc(&tmap_v);
+        const int row0 = seq_start + q0;
+        tc::mbar_expect_tx(bar(BAR_Q), (has_b ? 2 : 1) * kPfTileBytes);
+        for (int t = 0; t < (has_b ? 2 : 1); ++t)
+          for (int h = 0; h < 2; ++h)
+            tc::tma_load_3d(q_smem + t * kPfTileBytes + h * kPfHalfBytes, &tmap_q, 64 * h, head_a + t, row0, bar(BAR_Q));
+        for (int j = 0; j < n_kv; ++j) {
+          const int s = j % kPfStages;
+          const uint32_t ph = ((j / kPfStages) & 1) ^ 1;
+          const int krow = seq_start + j * kPfTile;
+          tc::mbar_wait(bar(BAR_KEMPTY + s), ph, abort_flag, p.error_word, 1);
+          tc::mbar_expect_tx(bar(BAR_KFULL + s), kPfTileBytes);
+          for (int h = 0; h < 2; ++h)
+            tc::tma_load_3d(k_smem + s * kPfTileBytes + h * kPfHalfBytes, &tmap_k, 64 * h, kvh, krow, bar(BAR_KFULL + s));
+          tc::mbar_wait(bar(BAR_VEMPTY + s), ph, abort_flag, p.error_word, 2);
+          tc::mbar_expect_tx(bar(BAR_VFULL + s), kPfTileBytes);
+          for (int h = 0; h < 2; ++h)
+            tc::tma_load_3d(v_smem + s * kPfTileBytes + h * kPfHalfBytes, &tmap_v, 64 * h, kvh, krow, bar(BAR_VFULL + s));
+        }
+      }
+    } else if (warp == 9) {
+      // ------------------------------- MMA issuer -------------------------------
+      if (lane == 0) {
+        const uint32_t idesc_qk = tc::instr_desc_f16(p.fmt, p.fmt, false, 128, 128);
+        // A and B must have the same format: fp16 P against bf16 V is rejected
+        // by the hardware as an illegal instruction.
+        const uint32_t idesc_pv = tc::instr_desc_f16(p.fmt, p.fmt, true, 128, 128);
+        const int nt = has_b ? 2 : 1;
+        auto issue_qk = [&](int t, int s) {
+#pragma unroll
+          for (int h = 0; h < 2; ++h)
+#pragma unroll
+            for (int ks = 0; ks < 4; ++ks) {
+              const uint64_t a = tc::smem_desc_sw128(q_smem + t * kPfTileBytes + h * kPfHalfBytes + ks * 32, 16, 1024);
+              const uint64_t b = tc::smem_desc_sw128(k_smem + s * kPfTileBytes + h * kPfHalfBytes + ks * 32, 16, 1024);
+              tc::mma_ss(tmem + t * 128, a, b, idesc_qk, (h | ks) != 0);
+            }
+        };
+        auto issue_pv = [&](int t, int s, bool accum, int p_col) {
+#pragma unroll
+          for (int ks = 0; ks < 8; ++ks) {
+            const uint64_t b = tc::smem_desc_sw128(v_smem + s * kPfTileBytes + ks * 2048, kPfHalfBytes, 1024);
+            tc::mma_ts(tmem + 256 + t * 128, tmem + t * 128 + p_col + ks * 8, b, idesc_pv, accum || ks != 0);
+          }
+        };
+        tc::mbar_wait(bar(BAR_Q), 0, abort_flag, p.error_word, 3);
+        tc::mbar_wait(bar(BAR_KFULL + 0), 0, abort_flag, p.error_word, 4);
+        tc::fence_after_sync();
+        for (int t = 0; t < nt; ++t) {
+          issue_qk(t, 0);
+          tc::mma_commit(bar(BAR_SFULL + t));
+        }
+        tc::mma_commit(bar(BAR_KEMPTY + 0));  // K stage 0 is free once QK(0) of both heads has run
+        for (int j = 0; j < n_kv; ++j) {
+          const int s = j % kPfStages;
+          const uint32_t ph = (j / kPfStages) & 1;
+          const bool more = j + 1 < n_kv;
+          const int s1 = (j + 1) % kPfStages;
+          tc::mbar_wait(bar(BAR_VFULL + s), ph, abort_flag, p.error_word, 5);
+          if (more) tc::mbar_wait(bar(BAR_KFULL + s1), ((j + 1) / kPfStages) & 1, abort_flag, p.error_word, 6);
+          for (int t = 0; t < nt; ++t) {
+            tc::mbar_wait(bar(BAR_PREADY + t), j & 1, abort_flag, p.error_word, 7);
+            tc::fence_after_sync();
+            issue_pv(t, s, j > 0, 0);
+            if (split_p) issue_pv(t, s, true, 64);   // residue of P, see the softmax warps
+            tc::mma_commit(bar(BAR_ODONE + t));
+            if (more) {
+              issue_qk(t, s1);
+              tc::mma_commit(bar(BAR_SFULL + t));
+            }
+          }
+          tc::mma_commit(bar(BAR_VEMPTY + s));     // both PV(j) done -> V stage free
+          if (more) tc::mma_commit(bar(BAR_KEMPTY + s1));               // QK(j+1) of both heads issued
+        }
+      }
+    }
+  } else {
+    // ------------------------------ softmax warps ------------------------------
+    const int t = warp >> 2;                       // 0: head A, 1: head B
+    if (t == 0 || has_b) {
+      const int row = (warp & 3) * 32 + lane;      // row of the tile = TMEM lane
+      const uint32_t lane_addr = static_cast<uint32_t>((warp & 3) * 32) << 16;
+      const uint32_t s_addr = tmem + lane_addr + t * 128;
+      const uint32_t o_addr = tmem + lane_addr + 256 + t * 128;
+      float m_used = -INFINITY, l = 0.f;
+      for (int j = 0; j < n_kv; ++j) {
+        tc::mbar_wait(bar(BAR_SFULL + t), j & 1, abort_flag, p.error_word, 8);
+        tc::fence_after_sync();
+        const bool diag = j == n_kv - 1;
+        // Pass 1: row maximum.  S is read from tensor memory twice (here and
+        // below) instead of being held in 128 registers.
+        float mx = -INFINITY;
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          uint32_t sv[32];
+          tc::tmem_ld32(s_addr + c * 32, sv);
+          tc::wait_ld();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            const float v = __uint_as_float(sv[i]);
+            mx = fmaxf(mx, (diag && c * 32 + i > row) ? -INFINITY : v);
+          }
+        }
+        mx *= p.scale_log2;  // scale > 0, so max commutes with it
+        // Move the reference maximum only when it grows by more than the
+        // threshold (or on the first tile): exp2 of at most 2^8 is harmless
+        // in fp32 and in bf16/fp16 P, and O rarely needs rescaling.
+        const bool grow = mx > m_used + kRescaleThreshold;
+        if (j > 0 && __any_sync(0xffffffffu, grow)) {
+          tc::mbar_wait(bar(BAR_ODONE + t), (j - 1) & 1, abort_flag, p.error_word, 9);
+          tc::fence_after_sync();
+          const float alpha = grow ? ex2(m_used - mx) : 1.f;
+#pragma unroll
+          for (int c = 0; c < 4; ++c) {
+            uint32_t ov[32];
+            tc::tmem_ld32(o_addr + c * 32, ov);
+            tc::wait_ld();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) ov[i] = __float_as_uint(__uint_as_float(ov[i]) * alpha);
+            tc::tmem_st32(o_addr + c * 32, ov);
+          }
+          tc::wait_st();
+          l *= alpha;
+        }
+        if (grow) m_used = mx;
+        float sum = 0.f;
+        uint32_t plo[32];
+#pragma unroll
+        for (int c2 = 0; c2 < 2; ++c2) {
+          uint32_t sa[32], sb[32], pk[32];
+          tc::tmem_ld32(s_addr + c2 * 64, sa);
+          tc::tmem_ld32(s_addr + c2 * 64 + 32, sb);
+          tc::wait_ld();
+          // All of S is in registers or consumed once the second half has been
+          // read: the residue of the first half can go over S columns 64..95.
+          if (c2 == 1 && split_p) tc::tmem_st32(s_addr + 64, plo);
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            const int k = (i & 15) * 2, col = c2 * 64 + 2 * i;
+            float s0 = __uint_as_float(i < 16 ? sa[k] : sb[k]);
+            float s1 = __uint_as_float(i < 16 ? sa[k + 1] : sb[k + 1]);
+            if (diag && col > row) s0 = -INFINITY;
+            if (diag && col + 1 > row) s1 = -INFINITY;
+            const float p0 = ex2(fmaf(s0, p.scale_log2, -m_used));
+            const float p1 = ex2(fmaf(s1, p.scale_log2, -m_used));
+            pk[i] = pack2<T>(p0, p1);
+            if constexpr (std::is_same<T, __nv_bfloat16>::value) {
+              const float h0 = __uint_as_float(pk[i] << 16), h1 = __uint_as_float(pk[i] & 0xffff0000u);
+              if (split_p) {
+                plo[i] = pack2<T>(p0 - h0, p1 - h1);
+                sum += p0 + p1;
+              } else {
+                // normalise by the sum of the ROUNDED weights, so that they still
+                // add up to one exactly: rounding perturbs the mix, not the scale
+                sum += h0 + h1;
+              }
+            } else {
+              sum += p0 + p1;
+            }
+          }
+          // P over the first 64 columns of S: columns 32*c2.. only cover S columns that were already read
+          tc::tmem_st32(s_addr + c2 * 32, pk);
+        }
+        if (split_p) tc::tmem_st32(s_addr + 96, plo);
+        l += sum;
+        tc::wait_st();
+        tc::fence_before_sync();
+        tc::mbar_arrive(bar(BAR_PREADY + t));
+      }
+      // ---- epilogue: O / l -> global ----
+      tc::mbar_wait(bar(BAR_ODONE + t), (n_kv - 1) & 1, abort_flag, p.error_word, 10);
+      tc::fence_after_sync();
+      const float inv_l = l > 0.f ? 1.f / l : 0.f;
+      const bool store = q0 + row < seq_len;
+      T* orow = static_cast<T*>(p.out) + static_cast<int64_t>(seq_start + q0 + row) * p.out_stride_tok +
+                static_cast<int64_t>(head_a + t) * kPfD;
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        uint32_t ov[32];
+        tc::tmem_ld32(o_addr + c * 32, ov);
+        tc::wait_ld();
+        if (store) {
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            uint4 w;
+            w.x = pack2<T>(__uint_as_float(ov[8 * i + 0]) * inv_l, __uint_as_float(ov[8 * i + 1]) * inv_l);
+            w.y = pack2<T>(__uint_as_float(ov[8 * i + 2]) * inv_l, __uint_as_float(ov[8 * i + 3]) * inv_l);
+            w.z = pack2<T>(__uint_as_float(ov[8 * i + 4]) * inv_l, __uint_as_float(ov[8 * i + 5]) * inv_l);
+            w.w = pack2<T>(__uint_as_float(ov[8 * i + 6]) * inv_l, __uint_as_float(ov[8 * i + 7]) * inv_l);
+            st_global16(orow + c * 32 + i * 8, w);
+          }
+        }
+      }
+    }
+  }
+  // ---- teardown: everyone is done with tensor memory before it is freed ----
+  tc::fence_before_sync();
+  __syncthreads();
+  if (warp == 8) {
+    tc::fence_after_sync();
+    tc::tmem_dealloc(tmem, 512);
+  }
+}
+
+// cuTensorMapEncodeTiled through the runtime's driver entry point (no link-time libcuda dependency).
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+static EncodeTiledFn encode_tiled_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (!fn) {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) == cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(ptr);
+    else
+      cudaGetLastError();
+  }
+  return fn;
+}
+
+// (tokens, heads, 128) tensor, token stride given; box = 64 elements x 1 head x 128 tokens, 128B swizzle.
+static int make_tmap(CUtensorMap* m, const void* base, int64_t tokens, int heads, int64_t stride_tok, int dtype) {
+  EncodeTiledFn fn = encode_tiled_fn();
+  if (!fn) return fail(MV_ERR_CUDA, "prefill: cuTensorMapEncodeTiled is not available");
+  const cuuint64_t dims[3] = {static_cast<cuuint64_t>(kPfD), static_cast<cuuint64_t>(heads),
+                              static_cast<cuuint64_t>(tokens)};
+  const cuuint64_t strides[2] = {static_cast<cuuint64_t>(kPfD) * 2, static_cast<cuuint64_t>(stride_tok) * 2};
+  const cuuint32_t box[3] = {64, 1, static_cast<cuuint32_t>(kPfTile)};
+  const cuuint32_t estr[3] = {1, 1, 1};
+  const CUresult r = fn(m, dtype == MV_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3,
+                        const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                        CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(MV_ERR_CUDA, "prefill: cuTensorMapEncodeTiled failed with %d", static_cast<int>(r));
+  return MV_OK;
+}
+
+}  // namespace mv
+
+extern "C" int mv_prefill_varlen(void* out, const void* q, const void* k, const void* v, int64_t q_stride_tok,
+                                 int64_t k_stride_tok, int64_t v_stride_tok, const int32_t* cu_seqlens, int num_seqs,
+                                 int64_t total_tokens, int num_heads, int num_kv_heads, int head_dim, float scale,
+                                 int* error_word, int dtype, void* stream) {
+  using namespace mv;
+  if (dtype != MV_F16 && dtype != MV_BF16) return fail(MV_ERR_DTYPE, "prefill: dtype %d", dtype);
+  if (num_seqs < 0 || total_tokens < 0 || num_heads <= 0 || num_kv_heads <= 0)
+    return fail(MV_ERR_SHAPE, "prefill: negative or zero size");
+  if (num_heads % num_kv_heads != 0)
+    return fail(MV_ERR_SHAPE, "prefill: num_heads %d is not a multiple of num_kv_heads %d", num_heads, num_kv_heads);
+  if (head_dim != kPfD) return fail(MV_ERR_SHAPE, "prefill: head_dim %d is not 128", head_dim);
+  if (num_seqs == 0 || total_tokens == 0) return MV_OK;
+  if (!out || !q || !k || !v || !cu_seqlens || !error_word) return fail(MV_ERR_NULL, "prefill: null pointer");
+  if (!aligned16(out) || !aligned16(q) || !aligned16(k) || !aligned16(v) || q_stride_tok % 8 || k_stride_tok % 8 ||
+      v_stride_tok % 8)
+    return fail(MV_ERR_ALIGN, "prefill: pointers and token strides must be 16-byte aligned");
+  if (q_stride_tok < static_cast<int64_t>(num_heads) * head_dim ||
+      k_stride_tok < static_cast<int64_t>(num_kv_heads) * head_dim ||
+      v_stride_tok < static_cast<int64_t>(num_kv_heads) * head_dim)
+    return fail(MV_ERR_SHAPE, "prefill: token stride smaller than a row");
+  if (total_tokens > 0x7fffffffLL) return fail(MV_ERR_LIMIT, "prefill: more than 2^31 tokens");
+
+  CUtensorMap tq, tk, tv;
+  int rc = make_tmap(&tq, q, total_tokens, num_heads, q_stride_tok, dtype);
+  if (rc) return rc;
+  if ((rc = make_tmap(&tk, k, total_tokens, num_kv_heads, k_stride_tok, dtype))) return rc;
+  if ((rc = make_tmap(&tv, v, total_tokens, num_kv_heads, v_stride_tok, dtype))) return rc;
+
+  PrefillParams p;
+  p.out = out;
+  p.out_stride_tok = static_cast<int64_t>(num_heads) * head_dim;
+  p.cu_seqlens = cu_seqlens;
+  p.num_seqs = num_seqs;
+  p.num_heads = num_heads;
+  p.num_kv_heads = num_kv_heads;
+  p.group = num_heads / num_kv_heads;
+  p.pairs = (p.group + 1) / 2;
+  p.scale_log2 = scale * 1.4426950408889634f;
+  p.fmt = dtype == MV_F16 ? 0 : 1;
+  p.error_word = error_word;
+  // Upper bound on the number of query tiles, from shapes only: no host sync.
+  const int64_t max_tiles = (total_tokens + kPfTile - 1) / kPfTile + num_seqs;
+  if (max_tiles > 0x7fffffffLL || static_cast<int64_t>(num_kv_heads) * p.pairs > 65535)
+    return fail(MV_ERR_LIMIT, "prefill: grid too large");
+  const dim3 grid(static_cast<unsigned>(max_tiles), static_cast<unsigned>(num_kv_heads * p.pairs));
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  static bool attr_done[64][2] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  const int ti = dtype == MV_F16 ? 0 : 1;
+  if (dev < 0 || dev >= 64 || !attr_done[dev][ti]) {
+    const cudaError_t e =
+        ti == 0 ? cudaFuncSetAttribute(prefill_varlen_kernel<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       kPfSmemBytes)
+                : cudaFuncSetAttribute(prefill_varlen_kernel<__nv_bfloat16>,
+                                       cudaFuncAttributeMaxDynamicSharedMemorySize, kPfSmemBytes);
+    if (e != cudaSuccess) {
+      cudaGetLastError();
+      return fail(MV_ERR_CUDA, "prefill: cudaFuncSetAttribute: %s", cudaGetErrorString(e));
+    }
+    if (dev >= 0 && dev < 64) attr_done[dev][ti] = true;
+  }
+  if (ti == 0) prefill_varlen_kernel<__half><<<grid, kPfThreads, kPfSmemBytes, st>>>(tq, tk, tv, p);
+  else prefill_varlen_kernel<__nv_bfloat16><<<grid, kPfThreads, kPfSmemBytes, st>>>(tq, tk, tv, p);
+  return check_launch("prefill_varlen_kernel");
+}

@@ -53,7 +53,33 @@ store_kv_copy_kernel(const uint4* __restrict__ key, const uint4* __restrict__ va
   }
 }
 
+// Exact code of one element, any scale: the definition evaluated with the
+// correctly rounded reciprocal and the exact remainder (see quant_chunk).
+__device__ __noinline__ int quant_exact(float x, float s) {
+  if (!(s > 0.f) || !(s < INFINITY)) return 0;
+  const float inv = __frcp_rn(s);
+  float n = rintf(x * inv);
+  const float r = fmaf(-n, s, x);
+  const float step = copysignf(1.f, r), half_s = 0.5f * s;
+  if (fabsf(r) > half_s) n += step;
+  else if (fabsf(r) == half_s && (static_cast<int>(n) & 1)) n += step;  // tie: to even
+  return static_cast<int>(fminf(fmaxf(n, -127.f), 127.f));
+}
+
 // Quantise 8 elements held in one 16-byte chunk; GROUP lanes share a head row.
+//
+// The codes must equal the CPU definition, rint(fp32(x / s)) clamped to
+// +-127, bit for bit.  x has at most 11 significant bits and s is an fp16
+// value, so the exact quotient is either a tie (k + 1/2) or at least 2^-19
+// (relative) away from one: the product with the correctly rounded reciprocal
+// (relative error 2^-23) rounds to the same integer as the quotient unless the
+// quotient is a tie.  Fast path, per element: multiply, round by adding
+// 1.5*2^23 (the code is then the low byte of the sum), and measure the
+// distance of the product from its rounded value; if any element of the
+// thread comes within 2^-10 of a half-integer, or the scale is not a normal
+// fp16 number (then |x/s| may exceed 127.5 and needs the clamp), all eight
+// elements take the exact path.  One IEEE division and one IEEE reciprocal per
+// head row (lane 0 of the group), none per element.
 template <typename T, int GROUP>
 __device__ __forceinline__ void quant_chunk(const uint4& raw, bool live, uint2& codes, __half& scale16) {
   float x[8];
@@ -69,19 +95,38 @@ __device__ __forceinline__ void quant_chunk(const uint4& raw, bool live, uint2& 
   for (int j = 0; j < 8; ++j) amax = fmaxf(amax, fabsf(x[j]));
 #pragma unroll
   for (int off = GROUP / 2; off > 0; off >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, off));
-  // IEEE division and round-to-nearest-even everywhere: the codes must equal
-  // the CPU restatement bit for bit.
-  scale16 = __float2half_rn(__fdiv_rn(amax, 127.f));
-  const float s = __half2float(scale16);
-  int q[8];
+  float s = 0.f, inv = 0.f;
+  if ((threadIdx.x & (GROUP - 1)) == 0) {
+    s = __half2float(__float2half_rn(__fdiv_rn(amax, 127.f)));
+    inv = (s >= 6.103515625e-05f && s < INFINITY) ? __frcp_rn(s) : 0.f;  // 0 marks "take the exact path"
+  }
+  const int leader = (threadIdx.x & 31) & ~(GROUP - 1);
+  s = __shfl_sync(0xffffffffu, s, leader);
+  inv = __shfl_sync(0xffffffffu, inv, leader);
+  scale16 = __float2half_rn(s);  // s is an fp16 value already: exact
+
+  constexpr float kMagic = 12582912.f;  // 1.5 * 2^23: adding it rounds to nearest-even integer
+  uint32_t t[8];
+  float worst = 0.f;
 #pragma unroll
   for (int j = 0; j < 8; ++j) {
-    float r = (s == 0.f) ? 0.f : rintf(__fdiv_rn(x[j], s));
-    r = fminf(fmaxf(r, -127.f), 127.f);
-    q[j] = static_cast<int>(r);
+    const float y = x[j] * inv;
+    const float tj = y + kMagic;
+    t[j] = __float_as_uint(tj);
+    worst = fmaxf(worst, fabsf(y - (tj - kMagic)));
   }
-  codes.x = (q[0] & 0xff) | ((q[1] & 0xff) << 8) | ((q[2] & 0xff) << 16) | ((q[3] & 0xff) << 24);
-  codes.y = (q[4] & 0xff) | ((q[5] & 0xff) << 8) | ((q[6] & 0xff) << 16) | ((q[7] & 0xff) << 24);
+  if (inv == 0.f || worst > 0.499f) {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) t[j] = static_cast<uint32_t>(quant_exact(x[j], s));
+  }
+  // low bytes of t[0..7] -> two words
+  uint32_t a01, a23;
+  asm("prmt.b32 %0, %1, %2, 0x0040;" : "=r"(a01) : "r"(t[0]), "r"(t[1]));
+  asm("prmt.b32 %0, %1, %2, 0x0040;" : "=r"(a23) : "r"(t[2]), "r"(t[3]));
+  asm("prmt.b32 %0, %1, %2, 0x5410;" : "=r"(codes.x) : "r"(a01), "r"(a23));
+  asm("prmt.b32 %0, %1, %2, 0x0040;" : "=r"(a01) : "r"(t[4]), "r"(t[5]));
+  asm("prmt.b32 %0, %1, %2, 0x0040;" : "=r"(a23) : "r"(t[6]), "r"(t[7]));
+  asm("prmt.b32 %0, %1, %2, 0x5410;" : "=r"(codes.y) : "r"(a01), "r"(a23));
 }
 
 // Fused scatter + int8 quantisation.  GROUP = head_dim/8 lanes form one head row.

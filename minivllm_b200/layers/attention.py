@@ -110,6 +110,19 @@ def paged_attention_decode(query, k_cache, v_cache, block_tables, context_lens, 
     if context_lens.dtype not in (torch.int32, torch.int64) or context_lens.numel() != batch or \
             not context_lens.is_contiguous():
         raise ValueError("context_lens must be a contiguous (batch,) int32 or int64 tensor")
+    quant = k_scale is not None or v_scale is not None
+    if quant:
+        if k_scale is None or v_scale is None:
+            raise ValueError("k_scale and v_scale must be given together")
+        if k_cache.dtype != torch.int8 or v_cache.dtype != torch.int8:
+            raise ValueError("int8 caches are required when scales are given")
+        for s in (k_scale, v_scale):
+            if s.dtype != torch.float16 or tuple(s.shape) != tuple(k_cache.shape[:3]) or not s.is_contiguous():
+                raise ValueError("scales must be contiguous fp16 tensors of shape (blocks, block_size, kv_heads)")
+    elif k_cache.dtype != query.dtype or v_cache.dtype != query.dtype:
+        raise ValueError(f"cache dtype {k_cache.dtype} differs from query dtype {query.dtype}")
+    if not (k_cache.is_contiguous() and v_cache.is_contiguous()):
+        raise ValueError("caches must be contiguous")
     if not query.is_contiguous():
         query = query.contiguous()
     out = torch.empty_like(query)
@@ -122,7 +135,6 @@ def paged_attention_decode(query, k_cache, v_cache, block_tables, context_lens, 
         raise ValueError("paged_attention_decode: invalid shape")
     if workspace is None:
         workspace = _decode_workspace(query.device, need)
-    quant = k_scale is not None
     rc = L.mv_paged_decode(
         out.data_ptr(), query.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(),
         k_scale.data_ptr() if quant else None, v_scale.data_ptr() if quant else None,
@@ -133,3 +145,104 @@ def paged_attention_decode(query, k_cache, v_cache, block_tables, context_lens, 
         _cabi.dtype_code(query.dtype), _cabi.stream_ptr())
     _cabi.check(rc)
     return out
+
+
+_error_words = {}
+
+
+def _error_word(device):
+    """One int32 per device that the prefill kernel sets when one of its bounded waits runs out."""
+    w = _error_words.get(device)
+    if w is None:
+        w = torch.zeros(1, dtype=torch.int32, device=device)
+        _error_words[device] = w
+    return w
+
+
+def prefill_error_code(device=None, clear=True):
+    """Reads (synchronising) the prefill kernel's error word; 0 means every wait completed."""
+    device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    w = _error_words.get(device)
+    if w is None:
+        return 0
+    code = int(w.item())
+    if code and clear:
+        w.zero_()
+    return code
+
+
+def flash_attention_prefill(q, k, v, cu_seqlens, scale, num_heads, num_kv_heads, head_dim):
+    """Causal attention over a packed batch of sequences (prefill).
+
+    q (tokens, heads, head_dim), k/v (tokens, kv_heads, head_dim), cu_seqlens
+    (num_seqs + 1,) int32 prefix sums.  Returns a new (tokens, heads, head_dim)
+    tensor.  Unlike the reference (src/myvllm/layers/attention.py:212-280)
+    there is no `.contiguous()` copy and no `cu_seqlens.cpu()` sync.
+    """
+    _cabi.require_cuda(q, k, v, cu_seqlens)
+    total = q.shape[0]
+    if tuple(q.shape) != (total, num_heads, head_dim) or tuple(k.shape) != (total, num_kv_heads, head_dim) or \
+            tuple(v.shape) != tuple(k.shape):
+        raise ValueError("q/k/v shapes do not match (tokens, heads, head_dim) / (tokens, kv_heads, head_dim)")
+    if cu_seqlens.dtype != torch.int32 or cu_seqlens.dim() != 1 or not cu_seqlens.is_contiguous():
+        raise ValueError("cu_seqlens must be a contiguous int32 vector")
+    if k.dtype != q.dtype or v.dtype != q.dtype:
+        raise ValueError("q, k and v dtypes differ")
+    out = torch.empty((total, num_heads, head_dim), dtype=q.dtype, device=q.device)
+    num_seqs = cu_seqlens.numel() - 1
+    if total == 0 or num_seqs <= 0:
+        return out
+    rc = _cabi.lib().mv_prefill_varlen(
+        out.data_ptr(), q.data_ptr(), k.data_ptr(), v.data_ptr(), _row_stride(q, "q"), _row_stride(k, "k"),
+        _row_stride(v, "v"), cu_seqlens.data_ptr(), num_seqs, total, num_heads, num_kv_heads, head_dim, float(scale),
+        _error_word(q.device).data_ptr(), _cabi.dtype_code(q.dtype), _cabi.stream_ptr())
+    _cabi.check(rc)
+    return out
+
+
+class Attention(nn.Module):
+    """Attention layer of the engine: stores the step's K/V into the paged cache
+    and runs varlen prefill or paged decode, as told by the global Context.
+
+    Same constructor arguments and attributes as the reference module
+    (src/myvllm/layers/attention.py:476-557); `k_cache` / `v_cache` start as
+    empty tensors and are assigned by the model runner's allocate_kv_cache,
+    which finds the modules by these two attribute names.  Optional
+    `k_scale` / `v_scale` attributes switch the layer to an int8 cache.
+    The cache's own block dimension is used for addressing; `block_size` is
+    only a default for callers that read it.
+    """
+
+    def __init__(self, num_heads: int, head_dim: int, scale: float = 1.0, num_kv_heads: int = None,
+                 block_size: int = 16):
+        super().__init__()
+        self.num_heads = num_heads
+        self.head_dim = head_dim
+        self.scale = scale
+        self.num_kv_heads = num_kv_heads if num_kv_heads is not None else num_heads
+        self.block_size = block_size
+        self.k_cache = self.v_cache = torch.tensor([])
+        self.k_scale = self.v_scale = None
+
+    def forward(self, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor) -> torch.Tensor:
+        ctx = get_context()
+        k_cache, v_cache = self.k_cache, self.v_cache
+        if q.dim() == 4:  # (B, N, heads, head_dim) -> packed tokens; decode passes N == 1
+            q = q.reshape(-1, q.shape[-2], q.shape[-1])
+            k = k.reshape(-1, k.shape[-2], k.shape[-1])
+            v = v.reshape(-1, v.shape[-2], v.shape[-1])
+        has_cache = k_cache.numel() > 0 and v_cache.numel() > 0
+        if has_cache and ctx.slot_mapping is not None:
+            store_kvcache(k, v, k_cache, v_cache, ctx.slot_mapping, k_cache.shape[1],
+                          k_scale=self.k_scale, v_scale=self.v_scale)
+        scale = self.scale / (self.head_dim ** 0.5)
+        if ctx.is_prefill:
+            if ctx.cu_seqlens_q is None:
+                raise ValueError("cu_seqlens_q must be provided for varlen attention")
+            o = flash_attention_prefill(q, k, v, ctx.cu_seqlens_q, scale, self.num_heads, self.num_kv_heads,
+                                        self.head_dim)
+        else:
+            o = paged_attention_decode(q, k_cache, v_cache, ctx.block_tables, ctx.context_lens, scale,
+                                       self.num_heads, self.num_kv_heads, self.head_dim, k_cache.shape[1],
+                                       k_scale=self.k_scale, v_scale=self.v_scale, workspace=ctx.decode_workspace)
+        return o.reshape(o.shape[0], self.num_heads * self.head_dim)

@@ -118,6 +118,14 @@ def test_store_int8_bit_exact_small(dtype, hd):
     d["k"][0] = 0            # zero row -> scale 0, codes 0
     d["k"][1] *= 1e-6        # subnormal fp16 scale
     d["v"][2] *= 1e-9        # scale underflows to 0
+    # exact ties: amax 127 -> scale 1.0, then k + 1/2 values must round to even
+    ties = torch.tensor([0.5, 1.5, 2.5, -0.5, -1.5, -2.5, 3.5, 12.5, 100.5, -100.5, 63.5, -64.5, 126.5, 127.0])
+    d["k"][3, 0, :14] = ties
+    d["k"][3, 0, 14:] = 0.25
+    d["v"][4, 1, :14] = ties * 0.5   # scale 0.5, same ties
+    d["v"][4, 1, 14:] = 0.125
+    if dtype == torch.bfloat16:
+        d["k"][5] *= 1e7             # amax/127 exceeds fp16 range: scale inf -> codes 0
     _run_quant(d, dtype)
 
 
