@@ -104,6 +104,34 @@ int mv_paged_decode(void* out, const void* q,
                     int dtype, void* stream);
 
 /*
+ * mv_paged_decode for callers that cannot allocate device memory.
+ * No counterpart in the reference (its Triton decode kernel needs no scratch
+ * because it never splits a sequence).  Same arguments and results as
+ * mv_paged_decode without `workspace`: the split-K scratch is a fixed array of
+ * mv_paged_decode_static_capacity() bytes (8 MiB) inside the library's device
+ * image, held by every GPU that loads the library.  Meant for a serving
+ * process that gave all free HBM to the KV pool and forbids later
+ * allocation, for code between stream-capture calls or in callbacks where the
+ * allocator must not run, and for bindings that only pass inputs and outputs.
+ * A problem needing more scratch than the array holds returns MV_ERR_LIMIT
+ * and launches nothing.  All calls on a device share the array: calls that
+ * overlap on the GPU race, so keep them on one stream or order them.  The
+ * first call on each device resolves the array's address (a host-side lookup)
+ * and should be made before any stream capture.  Neither function calls
+ * cudaMalloc, cudaFree or any allocating library routine.
+ */
+int64_t mv_paged_decode_static_capacity(void);
+int mv_paged_decode_static(void* out, const void* q,
+                           const void* k_cache, const void* v_cache,
+                           const void* k_scale, const void* v_scale,
+                           const int32_t* block_tables, int64_t bt_stride,
+                           int max_blocks,
+                           const void* context_lens, int ctx_is_i64,
+                           int batch, int num_heads, int num_kv_heads,
+                           int head_dim, int block_size, int64_t num_blocks,
+                           float scale, int dtype, void* stream);
+
+/*
  * Varlen causal prefill attention over a packed ragged batch.
  * Replaces: src/myvllm/layers/attention.py:212-280 `flash_attention_prefill`
  * and its Triton kernel :111-209.  Sequence s owns rows

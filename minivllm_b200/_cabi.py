@@ -30,6 +30,10 @@ SIGNATURES = {
     "mv_paged_decode": (_c_int, [_c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_i64, _c_int,
                                  _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_i64, _c_f32,
                                  _c_ptr, _c_i64, _c_int, _c_ptr]),
+    "mv_paged_decode_static_capacity": (_c_i64, []),
+    "mv_paged_decode_static": (_c_int, [_c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_i64, _c_int,
+                                        _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_i64, _c_f32,
+                                        _c_int, _c_ptr]),
     "mv_prefill_varlen": (_c_int, [_c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_i64, _c_i64, _c_i64, _c_ptr, _c_int, _c_i64,
                                    _c_int, _c_int, _c_int, _c_f32, _c_ptr, _c_int, _c_ptr]),
 }
