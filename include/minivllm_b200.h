@@ -111,7 +111,7 @@ int mv_paged_decode(void* out, const void* q,
  * mv_paged_decode_static_capacity() bytes (8 MiB) inside the library's device
  * image, held by every GPU that loads the library.  Meant for a serving
  * process that gave all free HBM to the KV pool and forbids later
- * allocation, for code between stream-capture calls or in callbacks where the
+ * allocation, for code in callbacks or latency-critical loops where the
  * allocator must not run, and for bindings that only pass inputs and outputs.
  * A problem needing more scratch than the array holds returns MV_ERR_LIMIT
  * and launches nothing.  All calls on a device share the array: calls that

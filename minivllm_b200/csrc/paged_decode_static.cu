@@ -5,9 +5,9 @@
 // whose KV range was split between CTAs, and its caller has to allocate that
 // buffer.  Some callers cannot: a serving process that handed all of its HBM
 // to the KV-cache pool at start-up and runs with allocation disabled, code
-// running inside a region where the allocator must not be touched (between
-// the capture calls of a stream, inside a callback), or a host binding that
-// was only ever given input and output pointers.  For them the scratch lives
+// running where the allocator must not be touched (a host callback, a
+// latency-critical loop that may not take the allocator's lock), or a host
+// binding that was only ever given input and output pointers.  For them the scratch lives
 // in a fixed array in device memory that is part of this library: every GPU
 // that loads the library holds kStaticScratchBytes until the process exits.
 //
