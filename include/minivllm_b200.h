@@ -153,6 +153,51 @@ int mv_prefill_varlen(void* out, const void* q, const void* k, const void* v,
                       int num_kv_heads, int head_dim, float scale,
                       int* error_word, int dtype, void* stream);
 
+/*
+ * Per-step metadata, built on the GPU from persistent per-sequence state.
+ * State (device memory, owned by the caller, one row per sequence "slot"):
+ *   tables (num_slots, max_blocks) int32 block table rows, -1 = none;
+ *   seq_len_state (num_slots) int32 tokens already in the cache;
+ *   last_token_state (num_slots) int64 last sampled token.
+ *
+ * mv_build_decode_meta replaces src/myvllm/engine/model_runner.py:231-256
+ * `prepare_decode` (and the per-layer positions of models/qwen3.py:210-212):
+ * for row b < *n_active with slot s and p = seq_len_state[s] it writes
+ * input_ids[b] = last_token_state[s], positions[b] = p, context_lens[b] = p+1,
+ * slot_mapping[b] = table[s][p/bs]*bs + p%bs, tables_out[b] = table[s], and
+ * bumps seq_len_state[s]; rows b >= *n_active (graph padding) get 0/0/0/-1
+ * and a table of -1.  n_active is read on the device so a captured graph can
+ * be replayed with any batch up to batch_padded.  A slot may appear once.
+ *
+ * mv_build_prefill_meta replaces model_runner.py:180-227 `prepare_prefill`
+ * (and qwen3.py:199-206): sequence i (slot seq_slots[i]) feeds tokens at
+ * positions num_cached[i] .. seq_lens[i]-1 (num_cached may be null = 0);
+ * writes cu_seqlens_q/k (num_seqs+1, int32), positions and slot_mapping
+ * (total_tokens, int64), last_token_index (num_seqs, int64) and sets
+ * seq_len_state[slot] = seq_lens[i].  total_tokens = sum of fed tokens.
+ *
+ * mv_update_block_tables applies `num_updates` (slot, index, block) int32
+ * triples to the table state (a sequence gained a block, or was allocated).
+ */
+int mv_build_decode_meta(const int32_t* seq_slots, const int32_t* n_active,
+                         int batch_padded, const int32_t* tables,
+                         int64_t tables_stride, int max_blocks, int block_size,
+                         int32_t* seq_len_state, const int64_t* last_token_state,
+                         int64_t* input_ids, int64_t* positions,
+                         int64_t* slot_mapping, int64_t* context_lens,
+                         int32_t* tables_out, int64_t out_stride, void* stream);
+int mv_build_prefill_meta(const int32_t* seq_slots, const int32_t* seq_lens,
+                          const int32_t* num_cached, int num_seqs,
+                          int64_t total_tokens, const int32_t* tables,
+                          int64_t tables_stride, int max_blocks, int block_size,
+                          int32_t* seq_len_state, int32_t* cu_seqlens_q,
+                          int32_t* cu_seqlens_k, int64_t* positions,
+                          int64_t* slot_mapping, int64_t* last_token_index,
+                          void* stream);
+int mv_update_block_tables(const int32_t* updates, int num_updates,
+                           int32_t* tables, int64_t tables_stride,
+                           int max_blocks, int num_slots, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -6,7 +6,8 @@
 // One CTA owns a 128-row query tile of one sequence for TWO query heads of the
 // same GQA group, so the two 128x128 problems share every K/V tile and the
 // tensor pipe always has the other head's MMAs to run while one head's
-// softmax is on the CUDA cores.  Roles (384 threads):
+// softmax is on the CUDA cores.  Roles (384 threads; the last warpgroup gives
+// most of its registers to the softmax warpgroups with setmaxnreg):
 //   warps 0-3   softmax of head A: thread i owns row i (= TMEM lane i)
 //   warps 4-7   softmax of head B
 //   warp  8     TMA producer: Q once, then K and V tiles through 2-stage rings
@@ -29,7 +30,7 @@
 
 namespace mv {
 
-constexpr int kPfThreads = 384;
+constexpr int kPfThreads = 384;  // 8 softmax warps + TMA warp + MMA warp + 2 idle warps (register donors)
 constexpr int kPfTile = 128;         // query rows and KV columns per tile
 constexpr int kPfD = 128;
 constexpr int kPfHalfBytes = kPfTile * 128;                 // one 64-element half of a 128-row tile
@@ -161,6 +162,7 @@ prefill_varlen_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
   const uint32_t tmem = s_tmem_base;
 
   if (warp >= 8) {
+    tc::setmaxnreg_dec_40();
     if (warp == 8) {
       // ------------------------------ TMA producer ------------------------------
       if (lane == 0) {
@@ -244,6 +246,7 @@ prefill_varlen_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
     }
   } else {
     // ------------------------------ softmax warps ------------------------------
+    tc::setmaxnreg_inc_232();
     const int t = warp >> 2;                       // 0: head A, 1: head B
     if (t == 0 || has_b) {
       const int row = (warp & 3) * 32 + lane;      // row of the tile = TMEM lane
@@ -251,85 +254,103 @@ prefill_varlen_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
       const uint32_t s_addr = tmem + lane_addr + t * 128;
       const uint32_t o_addr = tmem + lane_addr + 256 + t * 128;
       float m_used = -INFINITY, l = 0.f;
+      // Rare: the reference maximum of some row of this warp moved.  PV(j-1) must have landed in O
+      // before O is scaled; PV(j) cannot start before this warp arrives at PREADY below.
+      auto rescale_o = [&](float alpha, int j, float& l_ref) {
+        tc::mbar_wait(bar(BAR_ODONE + t), (j - 1) & 1, abort_flag, p.error_word, 9);
+        tc::fence_after_sync();
+#pragma unroll 1
+        for (int c = 0; c < 4; ++c) {
+          uint32_t ov[32];
+          tc::tmem_ld32(o_addr + c * 32, ov);
+          tc::wait_ld();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) ov[i] = __float_as_uint(__uint_as_float(ov[i]) * alpha);
+          tc::tmem_st32(o_addr + c * 32, ov);
+        }
+        tc::wait_st();
+        l_ref *= alpha;
+      };
       for (int j = 0; j < n_kv; ++j) {
         tc::mbar_wait(bar(BAR_SFULL + t), j & 1, abort_flag, p.error_word, 8);
         tc::fence_after_sync();
         const bool diag = j == n_kv - 1;
-        // Pass 1: row maximum.  S is read from tensor memory twice (here and
-        // below) instead of being held in 128 registers.
-        float mx = -INFINITY;
+        float sum = 0.f;
+        if (!split_p) {
+          // ---- fast path: the whole S row in registers, one wait for four loads ----
+          uint32_t sv[4][32];
 #pragma unroll
-        for (int c = 0; c < 4; ++c) {
-          uint32_t sv[32];
-          tc::tmem_ld32(s_addr + c * 32, sv);
+          for (int c = 0; c < 4; ++c) tc::tmem_ld32(s_addr + c * 32, sv[c]);
           tc::wait_ld();
+          if (diag) {
 #pragma unroll
-          for (int i = 0; i < 32; ++i) {
-            const float v = __uint_as_float(sv[i]);
-            mx = fmaxf(mx, (diag && c * 32 + i > row) ? -INFINITY : v);
+            for (int c = 0; c < 4; ++c)
+#pragma unroll
+              for (int i = 0; i < 32; ++i)
+                if (c * 32 + i > row) sv[c][i] = 0xff800000u;  // -inf
           }
-        }
-        mx *= p.scale_log2;  // scale > 0, so max commutes with it
-        // Move the reference maximum only when it grows by more than the
-        // threshold (or on the first tile): exp2 of at most 2^8 is harmless
-        // in fp32 and in bf16/fp16 P, and O rarely needs rescaling.
-        const bool grow = mx > m_used + kRescaleThreshold;
-        if (j > 0 && __any_sync(0xffffffffu, grow)) {
-          tc::mbar_wait(bar(BAR_ODONE + t), (j - 1) & 1, abort_flag, p.error_word, 9);
-          tc::fence_after_sync();
-          const float alpha = grow ? ex2(m_used - mx) : 1.f;
+          float mx = -INFINITY;
+#pragma unroll
+          for (int c = 0; c < 4; ++c)
+#pragma unroll
+            for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(sv[c][i]));
+          mx *= p.scale_log2;  // scale > 0, so max commutes with it
+          const bool grow = mx > m_used + kRescaleThreshold;
+          if (j > 0 && __any_sync(0xffffffffu, grow)) rescale_o(grow ? ex2(m_used - mx) : 1.f, j, l);
+          if (grow) m_used = mx;
+#pragma unroll
+          for (int c2 = 0; c2 < 2; ++c2) {
+            uint32_t pk[32];
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {
+              const int c = 2 * c2 + (i >> 4), k = (i & 15) * 2;
+              const float p0 = ex2(fmaf(__uint_as_float(sv[c][k]), p.scale_log2, -m_used));
+              const float p1 = ex2(fmaf(__uint_as_float(sv[c][k + 1]), p.scale_log2, -m_used));
+              sum += p0 + p1;
+              pk[i] = pack2<T>(p0, p1);
+            }
+            tc::tmem_st32(s_addr + c2 * 32, pk);   // P over the first 64 columns of S (all of S is in registers)
+          }
+        } else {
+          // ---- first query tile in bf16: two passes over S, P plus its rounding residue ----
+          float mx = -INFINITY;
 #pragma unroll
           for (int c = 0; c < 4; ++c) {
-            uint32_t ov[32];
-            tc::tmem_ld32(o_addr + c * 32, ov);
+            uint32_t sv[32];
+            tc::tmem_ld32(s_addr + c * 32, sv);
             tc::wait_ld();
 #pragma unroll
-            for (int i = 0; i < 32; ++i) ov[i] = __float_as_uint(__uint_as_float(ov[i]) * alpha);
-            tc::tmem_st32(o_addr + c * 32, ov);
+            for (int i = 0; i < 32; ++i)
+              mx = fmaxf(mx, (diag && c * 32 + i > row) ? -INFINITY : __uint_as_float(sv[i]));
           }
-          tc::wait_st();
-          l *= alpha;
-        }
-        if (grow) m_used = mx;
-        float sum = 0.f;
-        uint32_t plo[32];
+          m_used = mx * p.scale_log2;   // split_p implies a single KV tile: j == 0, nothing to rescale
+          uint32_t plo[32];
 #pragma unroll
-        for (int c2 = 0; c2 < 2; ++c2) {
-          uint32_t sa[32], sb[32], pk[32];
-          tc::tmem_ld32(s_addr + c2 * 64, sa);
-          tc::tmem_ld32(s_addr + c2 * 64 + 32, sb);
-          tc::wait_ld();
-          // All of S is in registers or consumed once the second half has been
-          // read: the residue of the first half can go over S columns 64..95.
-          if (c2 == 1 && split_p) tc::tmem_st32(s_addr + 64, plo);
+          for (int c2 = 0; c2 < 2; ++c2) {
+            uint32_t sa[32], sb[32], pk[32];
+            tc::tmem_ld32(s_addr + c2 * 64, sa);
+            tc::tmem_ld32(s_addr + c2 * 64 + 32, sb);
+            tc::wait_ld();
+            // once the second half of S has been read, the residue of the first half can go over columns 64..95
+            if (c2 == 1) tc::tmem_st32(s_addr + 64, plo);
 #pragma unroll
-          for (int i = 0; i < 32; ++i) {
-            const int k = (i & 15) * 2, col = c2 * 64 + 2 * i;
-            float s0 = __uint_as_float(i < 16 ? sa[k] : sb[k]);
-            float s1 = __uint_as_float(i < 16 ? sa[k + 1] : sb[k + 1]);
-            if (diag && col > row) s0 = -INFINITY;
-            if (diag && col + 1 > row) s1 = -INFINITY;
-            const float p0 = ex2(fmaf(s0, p.scale_log2, -m_used));
-            const float p1 = ex2(fmaf(s1, p.scale_log2, -m_used));
-            pk[i] = pack2<T>(p0, p1);
-            if constexpr (std::is_same<T, __nv_bfloat16>::value) {
-              const float h0 = __uint_as_float(pk[i] << 16), h1 = __uint_as_float(pk[i] & 0xffff0000u);
-              if (split_p) {
-                plo[i] = pack2<T>(p0 - h0, p1 - h1);
-                sum += p0 + p1;
-              } else {
-                // normalise by the sum of the ROUNDED weights, so that they still
-                // add up to one exactly: rounding perturbs the mix, not the scale
-                sum += h0 + h1;
-              }
-            } else {
+            for (int i = 0; i < 32; ++i) {
+              const int k = (i & 15) * 2, col = c2 * 64 + 2 * i;
+              float s0 = __uint_as_float(i < 16 ? sa[k] : sb[k]);
+              float s1 = __uint_as_float(i < 16 ? sa[k + 1] : sb[k + 1]);
+              if (diag && col > row) s0 = -INFINITY;
+              if (diag && col + 1 > row) s1 = -INFINITY;
+              const float p0 = ex2(fmaf(s0, p.scale_log2, -m_used));
+              const float p1 = ex2(fmaf(s1, p.scale_log2, -m_used));
+              pk[i] = pack2<T>(p0, p1);
+              const float2 hi = Elem<T>::to_f2(*reinterpret_cast<typename Elem<T>::T2*>(&pk[i]));
+              plo[i] = pack2<T>(p0 - hi.x, p1 - hi.y);
               sum += p0 + p1;
             }
+            tc::tmem_st32(s_addr + c2 * 32, pk);
           }
-          // P over the first 64 columns of S: columns 32*c2.. only cover S columns that were already read
-          tc::tmem_st32(s_addr + c2 * 32, pk);
+          tc::tmem_st32(s_addr + 96, plo);
         }
-        if (split_p) tc::tmem_st32(s_addr + 96, plo);
         l += sum;
         tc::wait_st();
         tc::fence_before_sync();

@@ -1,0 +1,250 @@
+"""Model runner: step metadata on the GPU, KV-cache allocation, eager prefill
+and CUDA-graph decode around the attention path.
+
+Same responsibilities and method names as the reference's
+src/myvllm/engine/model_runner.py (`prepare_prefill` :180, `prepare_decode`
+:231, `run_model` :267, `run` :298, `capture_cudagraph` :317,
+`allocate_kv_cache` :140), redesigned:
+  * metadata comes from device-resident sequence state (engine/metadata.py);
+    the host uploads slot ids only, never slot_mapping / block tables;
+  * one captured graph per padded batch size holds the WHOLE decode step:
+    metadata kernel, every layer, LM head, sampling and the write-back of the
+    sampled token into the device state — a replay needs no host-built tensor
+    and its only host traffic is the batch of sampled token ids coming back;
+  * tensor parallelism is SPMD: every rank runs this same runner on its own
+    GPU and makes the same scheduling decisions from the same sampled tokens,
+    so the reference's shared-memory RPC to worker processes is not needed.
+    The only collectives are the NCCL all-reduces inside the model.
+"""
+import math
+
+import torch
+import torch.distributed as dist
+
+from ..utils.context import get_context, reset_context, set_context
+from .metadata import SequenceStateTable
+from .qwen3 import Qwen3Config, Qwen3ForCausalLM
+
+
+def _cfg(config, *names, default=None):
+    for n in names:
+        if n in config:
+            return config[n]
+    return default
+
+
+class ModelRunner:
+    def __init__(self, config: dict, rank: int = 0, world_size: int = None, device=None, model=None):
+        self.config = config
+        self.rank = rank
+        self.world_size = world_size if world_size is not None else config.get("world_size", 1)
+        self.block_size = config.get("block_size", 256)
+        self.enforce_eager = config.get("enforce_eager", False)
+        self.max_num_seqs = _cfg(config, "max_num_seqs", "max_num_sequences", default=16)
+        self.max_num_batched_tokens = _cfg(config, "max_num_batched_tokens", "max_num_batch_tokens", default=1024)
+        self.max_model_len = _cfg(config, "max_model_length", "max_position", default=4096)
+        self.dtype = config.get("dtype", torch.bfloat16)
+        self.device = torch.device(device if device is not None else f"cuda:{torch.cuda.current_device()}")
+        self.greedy = config.get("greedy", False)
+        mcfg = Qwen3Config.from_dict(config)
+        mcfg.max_position = max(mcfg.max_position, self.max_model_len)
+        self.model_cfg = mcfg
+        self.model = model if model is not None else Qwen3ForCausalLM(
+            mcfg, tp_rank=rank, tp_size=self.world_size, dtype=self.dtype, device=self.device,
+            seed=config.get("seed", 0))
+        self.max_blocks_per_seq = math.ceil(self.max_model_len / self.block_size)
+        # one spare slot: padded rows of a captured batch point at it
+        self.num_slots = self.max_num_seqs + 1
+        self.pad_slot = self.max_num_seqs
+        self.state = SequenceStateTable(self.num_slots, self.max_blocks_per_seq, self.block_size, self.device)
+        # the default CUDA generator is the one CUDA graphs know how to replay; same seed on every TP rank
+        torch.cuda.manual_seed(config.get("sample_seed", 1234))
+        self.graphs, self.graph_vars = {}, None
+        self.decode_workspace = None
+        self.allocate_kv_cache()
+        if not self.enforce_eager:
+            self.capture_cudagraph()
+
+    # ------------------------------------------------------------------ memory ---
+    def kv_block_bytes(self):
+        c = self.model_cfg
+        return self.block_size * 2 * c.num_layers * (c.num_kv_heads // self.world_size) * c.head_dim * \
+            torch.empty((), dtype=self.dtype).element_size()
+
+    def allocate_kv_cache(self):
+        """One pool (2, layers, blocks, block_size, kv_heads/tp, head_dim); every module that has
+        `k_cache` and `v_cache` attributes gets its layer's views (the reference's duck typing,
+        model_runner.py:162-168)."""
+        c = self.model_cfg
+        if "num_kv_blocks" in self.config:
+            num_blocks = int(self.config["num_kv_blocks"])
+        else:
+            free, _ = torch.cuda.mem_get_info(self.device)
+            util = self.config.get("gpu_memory_utilization", 0.9)
+            reserve = self.config.get("activation_reserve_bytes", self._activation_reserve())
+            num_blocks = int((free * util - reserve) // self.kv_block_bytes())
+            if self.world_size > 1:  # every rank must agree on the pool size: the scheduler state is replicated
+                t = torch.tensor([num_blocks], device=self.device, dtype=torch.int64)
+                dist.all_reduce(t, op=dist.ReduceOp.MIN)
+                num_blocks = int(t.item())
+        assert num_blocks >= 1, f"not enough memory for one KV block on rank {self.rank}"
+        self.num_kv_blocks = num_blocks
+        self.kv_cache = torch.zeros(2, c.num_layers, num_blocks, self.block_size, c.num_kv_heads // self.world_size,
+                                    c.head_dim, dtype=self.dtype, device=self.device)
+        layer = 0
+        for module in self.model.modules():
+            if hasattr(module, "k_cache") and hasattr(module, "v_cache"):
+                module.k_cache = self.kv_cache[0, layer]
+                module.v_cache = self.kv_cache[1, layer]
+                layer += 1
+        assert layer == c.num_layers
+
+    def _activation_reserve(self):
+        """Peak activation bytes of the largest prefill wave (logits of the last tokens included), estimated
+        from shapes instead of the reference's warm-up run."""
+        c, t = self.model_cfg, self.max_num_batched_tokens
+        per_tok = (c.hidden_size * 6 + (c.num_heads + 2 * c.num_kv_heads) * c.head_dim * 3 // self.world_size +
+                   3 * c.intermediate_size * 2 // self.world_size) * 4
+        return t * per_tok + self.max_num_seqs * c.vocab_size * 8 + (2 << 30)
+
+    # ---------------------------------------------------------------- metadata ---
+    def _sync_tables(self, seqs):
+        """Block-table entries the device rows do not hold yet (new sequences, sequences that grew)."""
+        upd = []
+        for s in seqs:
+            if s.synced_blocks == 0 and s.block_table:
+                row = list(s.block_table) + [-1] * (self.max_blocks_per_seq - len(s.block_table))
+                upd.extend((s.slot, i, b) for i, b in enumerate(row))
+            else:
+                upd.extend((s.slot, i, s.block_table[i]) for i in range(s.synced_blocks, len(s.block_table)))
+            s.synced_blocks = len(s.block_table)
+        self.state.update_tables(upd)
+
+    def prepare_prefill(self, seqs):
+        self._sync_tables(seqs)
+        ids = [t for s in seqs for t in s.token_ids[s.num_cached_tokens:]]
+        input_ids = torch.tensor(ids, dtype=torch.int64).pin_memory().to(self.device, non_blocking=True)
+        meta = self.state.build_prefill([s.slot for s in seqs], [len(s) for s in seqs],
+                                        [s.num_cached_tokens for s in seqs])
+        set_context(True, meta["cu_seqlens_q"], meta["cu_seqlens_k"], meta["max_seqlen_q"], meta["max_seqlen_k"],
+                    meta["slot_mapping"], None, None, positions=meta["positions"],
+                    last_token_index=meta["last_token_index"])
+        return input_ids
+
+    def _upload_slots(self, seqs, slots_buf, n_active_buf):
+        bp = slots_buf.shape[0]
+        host = torch.full((bp + 1,), self.pad_slot, dtype=torch.int32)
+        host[:len(seqs)] = torch.tensor([s.slot for s in seqs], dtype=torch.int32)
+        host[bp] = len(seqs)
+        dev = host.pin_memory().to(self.device, non_blocking=True)
+        slots_buf.copy_(dev[:bp])
+        n_active_buf.copy_(dev[bp:])
+
+    def prepare_decode(self, seqs, bufs=None, slots_buf=None, n_active_buf=None):
+        """Eager form: allocates the step's buffers; the graph path passes its static ones."""
+        self._sync_tables(seqs)
+        if bufs is None:
+            bp = len(seqs)
+            bufs = self.state.new_decode_buffers(bp)
+            slots_buf = torch.empty(bp, dtype=torch.int32, device=self.device)
+            n_active_buf = torch.empty(1, dtype=torch.int32, device=self.device)
+        self._upload_slots(seqs, slots_buf, n_active_buf)
+        self.state.build_decode(slots_buf, n_active_buf, bufs)
+        self._set_decode_context(bufs)
+        return bufs["input_ids"], slots_buf
+
+    def _set_decode_context(self, bufs):
+        set_context(False, None, None, 0, 0, bufs["slot_mapping"], bufs["context_lens"], bufs["block_tables"],
+                    positions=bufs["positions"], decode_workspace=self.decode_workspace)
+
+    # ---------------------------------------------------------------- sampling ---
+    def sample(self, logits, temperatures=None):
+        """Greedy argmax, or the reference's exponential-race draw (src/myvllm/layers/sampler.py:15-19)."""
+        if self.greedy or temperatures is None:
+            return logits.argmax(dim=-1)
+        probs = torch.softmax(logits.float() / temperatures.unsqueeze(-1), dim=-1)
+        noise = torch.empty_like(probs).exponential_(1).clamp_min_(1e-10)
+        return probs.div_(noise).argmax(dim=-1)
+
+    # --------------------------------------------------------------------- run ---
+    @torch.inference_mode()
+    def run_model(self, input_ids, is_prefill):
+        return self.model.compute_logits(self.model(input_ids))
+
+    @torch.inference_mode()
+    def run(self, seqs, is_prefill):
+        temps = None
+        if not self.greedy:
+            temps = torch.tensor([s.temperature for s in seqs], dtype=torch.float32).pin_memory().to(
+                self.device, non_blocking=True)
+        if is_prefill:
+            input_ids = self.prepare_prefill(seqs)
+            tokens = self.sample(self.run_model(input_ids, True), temps)
+            slots = torch.tensor([s.slot for s in seqs], dtype=torch.int64).pin_memory().to(self.device,
+                                                                                             non_blocking=True)
+            self.state.last_token.index_copy_(0, slots, tokens)
+        elif self.enforce_eager or not self.graphs:
+            input_ids, slots_buf = self.prepare_decode(seqs)
+            tokens = self.sample(self.run_model(input_ids, False), temps)
+            self.state.last_token.index_copy_(0, slots_buf.long(), tokens)
+        else:
+            tokens = self._replay(seqs, temps)
+        out = tokens[:len(seqs)].tolist()          # the step's only device->host read
+        reset_context()
+        return out
+
+    # ------------------------------------------------------------------ graphs ---
+    def _decode_body(self, v, bp):
+        """The whole decode step on static buffers; captured once per padded batch size."""
+        bufs = {k: t[:bp] for k, t in v["bufs"].items()}
+        self.state.build_decode(v["slots"][:bp], v["n_active"], bufs)
+        self._set_decode_context(bufs)
+        logits = self.model.compute_logits(self.model(bufs["input_ids"]))
+        tokens = self.sample(logits, None if self.greedy else v["temps"][:bp])
+        v["tokens"][:bp].copy_(tokens)
+        self.state.last_token.index_copy_(0, v["slots"][:bp].long(), tokens)
+
+    @torch.inference_mode()
+    def capture_cudagraph(self):
+        max_bs = self.max_num_seqs
+        v = dict(bufs=self.state.new_decode_buffers(max_bs),
+                 slots=torch.full((max_bs,), self.pad_slot, dtype=torch.int32, device=self.device),
+                 n_active=torch.zeros(1, dtype=torch.int32, device=self.device),
+                 temps=torch.ones(max_bs, dtype=torch.float32, device=self.device),
+                 tokens=torch.zeros(max_bs, dtype=torch.int64, device=self.device))
+        c = self.model_cfg
+        from .. import _cabi
+        need = _cabi.lib().mv_paged_decode_workspace_bytes(max_bs, c.num_heads // self.world_size,
+                                                           c.num_kv_heads // self.world_size, c.head_dim,
+                                                           self.max_blocks_per_seq, self.block_size)
+        self.decode_workspace = torch.empty(max(need, 1), dtype=torch.uint8, device=self.device)
+        sizes = [b for b in [1, 2, 4, 8] if b <= max_bs] + list(range(16, max_bs + 1, 16))
+        if max_bs not in sizes:
+            sizes.append(max_bs)
+        self.graph_vars, pool = v, None
+        # n_active = 0 during warm-up and capture: every row is padding, no sequence state is touched
+        for bp in sorted(set(sizes), reverse=True):
+            self._decode_body(v, bp)               # warm-up (also resolves lazy initialisation)
+            torch.cuda.synchronize()
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, pool=pool):
+                self._decode_body(v, bp)
+            pool = pool or g.pool()
+            self.graphs[bp] = g
+        torch.cuda.synchronize()
+        reset_context()
+
+    def _replay(self, seqs, temps):
+        bs = len(seqs)
+        bp = next(b for b in sorted(self.graphs) if b >= bs)
+        v = self.graph_vars
+        self._sync_tables(seqs)
+        self._upload_slots(seqs, v["slots"][:bp], v["n_active"])
+        if temps is not None:
+            v["temps"][:bs].copy_(temps)
+        self.graphs[bp].replay()
+        return v["tokens"]
+
+    def exit(self):
+        self.graphs, self.graph_vars = {}, None
+        torch.cuda.synchronize()

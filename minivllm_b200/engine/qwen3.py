@@ -1,0 +1,170 @@
+"""Qwen3-shaped decoder used as the HARNESS that drives the attention path at
+engine level (BASELINE configurations 3 and 4).  Everything here except the
+`Attention` module is plain torch (cuBLAS GEMMs, torch's fused rms_norm) —
+library code, out of the hot path's scope — with the tensor-parallel layout of
+the reference (src/myvllm/models/qwen3.py, src/myvllm/layers/linear.py:83-221):
+query/KV heads and the MLP are split across ranks, the only collectives are the
+all-reduces after o_proj and down_proj, embedding and LM head are replicated.
+
+Differences from the reference model, all forced by its defects: RoPE is
+computed in fp32 and cast back to the model dtype (the reference promotes q/k
+to fp32 and then fails in o_proj); positions come from the Context, built once
+per step on the GPU (the reference rebuilds them on the host in every layer);
+weights are seeded (the reference leaves them uninitialised).  Kept as in the
+reference: RMSNorm eps 1e-5 whatever the config says, one shared gamma for the
+q and k norms, tied embeddings when asked.
+"""
+import math
+from dataclasses import dataclass
+
+import torch
+import torch.nn as nn
+import torch.nn.functional as F
+
+from ..layers.attention import Attention
+from ..utils.context import get_context
+
+RMS_EPS = 1e-5
+
+
+@dataclass
+class Qwen3Config:
+    vocab_size: int = 151936
+    hidden_size: int = 1024
+    num_layers: int = 8
+    num_heads: int = 16
+    num_kv_heads: int = 8
+    head_dim: int = 128
+    intermediate_size: int = 3072
+    rope_theta: float = 1e6
+    max_position: int = 4096
+    tie_word_embeddings: bool = True
+    scale: float = 1.0
+    block_size: int = 256
+
+    @staticmethod
+    def from_dict(c):
+        return Qwen3Config(vocab_size=c["vocab_size"], hidden_size=c["hidden_size"], num_layers=c["num_layers"],
+                           num_heads=c["num_heads"], num_kv_heads=c["num_kv_heads"],
+                           head_dim=c.get("head_dim", c["hidden_size"] // c["num_heads"]),
+                           intermediate_size=c["intermediate_size"], rope_theta=c.get("base", 1e6),
+                           max_position=c.get("max_position", c.get("max_model_length", 4096)),
+                           tie_word_embeddings=c.get("tie_word_embeddings", True), scale=c.get("scale", 1.0),
+                           block_size=c.get("block_size", 256))
+
+
+def _seeded_normal(shape, seed, device, std=0.02):
+    """N(0, std) in fp32 from a generator keyed by `seed`: the FULL tensor, so that every
+    tensor-parallel degree slices the same weights."""
+    g = torch.Generator(device=device).manual_seed(seed)
+    return torch.randn(shape, generator=g, device=device, dtype=torch.float32) * std
+
+
+def _rope_cache(head_dim, max_position, theta, device):
+    inv = 1.0 / (theta ** (torch.arange(0, head_dim, 2, dtype=torch.float32, device=device) / head_dim))
+    ang = torch.arange(max_position, dtype=torch.float32, device=device)[:, None] * inv[None, :]
+    return torch.cos(ang), torch.sin(ang)  # (max_position, head_dim/2) each
+
+
+def apply_rope(x, cos, sin):
+    """Rotate-half (neox) RoPE in fp32 on (tokens, heads, head_dim); cos/sin (tokens, head_dim/2)."""
+    xf = x.float()
+    x1, x2 = xf.chunk(2, dim=-1)
+    c, s = cos[:, None, :], sin[:, None, :]
+    return torch.cat([x1 * c - x2 * s, x2 * c + x1 * s], dim=-1).to(x.dtype)
+
+
+class DecoderLayer(nn.Module):
+    def __init__(self, cfg, layer, tp_rank, tp_size, dtype, device, seed):
+        super().__init__()
+        H, KVH, D, hid, inter = cfg.num_heads, cfg.num_kv_heads, cfg.head_dim, cfg.hidden_size, cfg.intermediate_size
+        assert H % tp_size == 0 and KVH % tp_size == 0 and inter % tp_size == 0, "tp must divide heads and MLP"
+        self.h, self.kvh, self.d, self.inter = H // tp_size, KVH // tp_size, D, inter // tp_size
+        self.tp_size = tp_size
+        base = seed * 1000003 + layer * 101
+        r = tp_rank
+        # column-parallel: rows of the (out, in) weight are sliced by head / by MLP column
+        q_full = _seeded_normal((H * D, hid), base + 1, device)
+        k_full = _seeded_normal((KVH * D, hid), base + 2, device)
+        v_full = _seeded_normal((KVH * D, hid), base + 3, device)
+        self.qkv_w = nn.Parameter(torch.cat([q_full[r * self.h * D:(r + 1) * self.h * D],
+                                             k_full[r * self.kvh * D:(r + 1) * self.kvh * D],
+                                             v_full[r * self.kvh * D:(r + 1) * self.kvh * D]]).to(dtype),
+                                  requires_grad=False)
+        del q_full, k_full, v_full
+        # row-parallel: columns of the (out, in) weight are sliced
+        o_full = _seeded_normal((hid, H * D), base + 4, device)
+        self.o_w = nn.Parameter(o_full[:, r * self.h * D:(r + 1) * self.h * D].contiguous().to(dtype),
+                                requires_grad=False)
+        del o_full
+        gate_full = _seeded_normal((inter, hid), base + 5, device)
+        up_full = _seeded_normal((inter, hid), base + 6, device)
+        self.gate_up_w = nn.Parameter(torch.cat([gate_full[r * self.inter:(r + 1) * self.inter],
+                                                 up_full[r * self.inter:(r + 1) * self.inter]]).to(dtype),
+                                      requires_grad=False)
+        del gate_full, up_full
+        down_full = _seeded_normal((hid, inter), base + 7, device)
+        self.down_w = nn.Parameter(down_full[:, r * self.inter:(r + 1) * self.inter].contiguous().to(dtype),
+                                   requires_grad=False)
+        del down_full
+        ones = lambda n: nn.Parameter(torch.ones(n, dtype=dtype, device=device), requires_grad=False)
+        self.input_norm_w, self.post_norm_w, self.qk_norm_w = ones(hid), ones(hid), ones(D)
+        self.attn = Attention(self.h, D, cfg.scale, self.kvh, cfg.block_size)
+
+    def forward(self, x, residual, cos, sin):
+        residual = x if residual is None else residual + x
+        h = F.rms_norm(residual, (residual.shape[-1],), self.input_norm_w, RMS_EPS)
+        qkv = F.linear(h, self.qkv_w)
+        q, k, v = qkv.split([self.h * self.d, self.kvh * self.d, self.kvh * self.d], dim=-1)
+        q = F.rms_norm(q.reshape(-1, self.h, self.d), (self.d,), self.qk_norm_w, RMS_EPS)
+        k = F.rms_norm(k.reshape(-1, self.kvh, self.d), (self.d,), self.qk_norm_w, RMS_EPS)
+        q, k = apply_rope(q, cos, sin), apply_rope(k, cos, sin)
+        o = self.attn(q, k, v.view(-1, self.kvh, self.d))     # v stays a strided view of qkv
+        o = F.linear(o, self.o_w)
+        if self.tp_size > 1:
+            torch.distributed.all_reduce(o)
+        residual = residual + o
+        h = F.rms_norm(residual, (residual.shape[-1],), self.post_norm_w, RMS_EPS)
+        gu = F.linear(h, self.gate_up_w)
+        act = F.silu(gu[:, :self.inter]) * gu[:, self.inter:]
+        out = F.linear(act, self.down_w)
+        if self.tp_size > 1:
+            torch.distributed.all_reduce(out)
+        return out, residual
+
+
+class Qwen3ForCausalLM(nn.Module):
+    def __init__(self, cfg: Qwen3Config, tp_rank=0, tp_size=1, dtype=torch.bfloat16, device="cuda", seed=0):
+        super().__init__()
+        self.cfg, self.tp_size, self.dtype = cfg, tp_size, dtype
+        self.embed = nn.Parameter(_seeded_normal((cfg.vocab_size, cfg.hidden_size), seed * 1000003 + 900001,
+                                                 device).to(dtype), requires_grad=False)
+        if cfg.tie_word_embeddings:
+            self.lm_head = self.embed
+        else:
+            self.lm_head = nn.Parameter(_seeded_normal((cfg.vocab_size, cfg.hidden_size), seed * 1000003 + 900002,
+                                                       device).to(dtype), requires_grad=False)
+        self.layers = nn.ModuleList(DecoderLayer(cfg, l, tp_rank, tp_size, dtype, device, seed)
+                                    for l in range(cfg.num_layers))
+        self.final_norm_w = nn.Parameter(torch.ones(cfg.hidden_size, dtype=dtype, device=device), requires_grad=False)
+        cos, sin = _rope_cache(cfg.head_dim, cfg.max_position, cfg.rope_theta, device)
+        self.register_buffer("rope_cos", cos, persistent=False)
+        self.register_buffer("rope_sin", sin, persistent=False)
+
+    def forward(self, input_ids):
+        """input_ids (tokens,) int64 -> hidden (tokens, hidden).  Positions come from the Context."""
+        positions = get_context().positions
+        if positions is None:
+            raise ValueError("Context.positions must be set before the model runs")
+        cos, sin = self.rope_cos[positions], self.rope_sin[positions]
+        x, residual = F.embedding(input_ids, self.embed), None
+        for layer in self.layers:
+            x, residual = layer(x, residual, cos, sin)
+        return F.rms_norm(residual + x, (x.shape[-1],), self.final_norm_w, RMS_EPS)
+
+    def compute_logits(self, hidden):
+        """Prefill keeps the last token of every sequence (Context.last_token_index); decode keeps all rows."""
+        ctx = get_context()
+        if ctx.is_prefill and ctx.last_token_index is not None:
+            hidden = hidden[ctx.last_token_index]
+        return F.linear(hidden, self.lm_head)

@@ -96,5 +96,66 @@ def main():
         print(name, kc.shape)
 
 
+
+
+# ---------------------------------------------------------------------------
+# Step metadata: the reference's Sequence / BlockManager / ModelRunner.prepare_*
+# run on the CPU (torch.tensor(pin_memory=...) and Tensor.cuda are shimmed).
+# ---------------------------------------------------------------------------
+METADATA_CASES = {
+    # block_size, prompts (token id lists), tokens appended afterwards (one decode step each)
+    "metadata_bs4": dict(block_size=4, prompts=[list(range(1, 11)), list(range(1, 9)) + [42], [7, 7, 7]],
+                         appended=[[11], [12], [13]]),
+    "metadata_bs16": dict(block_size=16, prompts=[list(range(100, 137)), list(range(5)), list(range(300, 331))],
+                          appended=[[1, 2], [3, 4], [5, 6]]),
+}
+
+
+def metadata_main():
+    import types
+    from myvllm.engine import model_runner as mr
+    from myvllm.engine.block_manager import BlockManager
+    from myvllm.engine.sequence import Sequence
+    from myvllm.utils.context import get_context
+
+    real_tensor = torch.tensor
+    mr.torch.tensor = lambda *a, **k: real_tensor(*a, **{x: y for x, y in k.items() if x != "pin_memory"})
+    torch.Tensor.cuda = lambda self, *a, **k: self
+    try:
+        for name, case in METADATA_CASES.items():
+            bs = case["block_size"]
+            Sequence.block_size = bs
+            bm = BlockManager(64, bs)
+            seqs = [Sequence(token_ids=list(p)) for p in case["prompts"]]
+            for s in seqs:
+                bm.allocate(s)
+            stub = types.SimpleNamespace(block_size=bs)
+            out = {}
+            ids = mr.ModelRunner.prepare_prefill(stub, seqs)
+            c = get_context()
+            out.update(prefill_input_ids=ids.numpy(), prefill_cu_q=c.cu_seqlens_q.numpy(),
+                       prefill_cu_k=c.cu_seqlens_k.numpy(), prefill_slot_mapping=c.slot_mapping.numpy(),
+                       prefill_num_cached=np.array([s.num_cached_tokens for s in seqs]),
+                       prefill_tables=np.array([s.block_table + [-1] * (8 - len(s.block_table)) for s in seqs]))
+            steps = len(case["appended"][0])
+            for t in range(steps):
+                for s, extra in zip(seqs, case["appended"]):
+                    s.append_token(extra[t])      # the intended postprocess (the reference appends to token_ids only)
+                    bm.append(s) if bm.can_append(s) else None
+                ids = mr.ModelRunner.prepare_decode(stub, seqs)
+                c = get_context()
+                out[f"decode{t}_input_ids"] = ids.numpy()
+                out[f"decode{t}_context_lens"] = c.context_lens.numpy()
+                out[f"decode{t}_slot_mapping"] = c.slot_mapping.numpy()
+                out[f"decode{t}_block_tables"] = c.block_tables.numpy()
+                out[f"decode{t}_tables_full"] = np.array([s.block_table + [-1] * (8 - len(s.block_table)) for s in seqs])
+            np.savez_compressed(os.path.join(HERE, name + ".npz"), case=repr(case), **out)
+            print(name, sorted(out))
+    finally:
+        mr.torch.tensor = real_tensor
+
+
 if __name__ == "__main__":
-    main()
+    if "--metadata-only" not in sys.argv:
+        main()
+    metadata_main()
