@@ -1,20 +1,33 @@
 #!/usr/bin/env python
-"""Benchmark of the ragged-batch attention hot path on B200.
+"""Benchmark of the ragged-batch attention path on B200.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload decode]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload engine|decode]
 
-Prints ONE JSON line (rank 0).  A step is one paged-decode call over the whole
-batch.  `value` is measured with the inputs resident in HBM; `e2e` is the same
-call through the public Python operator with the per-step host tensors
-(q, block tables, context lens) copied from pinned memory and the output
-copied back, inside the timed region.  `--impl reference` times the CPU path
-(the oracle's restatement of the reference's PyTorch decode) on a bounded
-sample of the same workload.
+Prints ONE JSON line (rank 0).
+
+--workload engine (default): engine output tokens/s.  Random-init Qwen3-8B-shaped
+  model (hidden 4096, 36 layers, 32 q / 8 kv heads, head_dim 128, SwiGLU 12288,
+  bf16), tensor parallel over the N GPUs (heads and MLP sharded, NCCL all-reduce
+  after o_proj / down_proj), 512 requests of random token ids with prompt
+  lengths uniform in [512, 1536], 512 greedy output tokens each, KV cache = 80 %
+  of free HBM, continuous batching.  A step is one `generate()` over all 512
+  requests (prefill waves included); value = output tokens / time.  Fixed total
+  work as N grows: "strong" scaling.  `e2e` is the same run clocked on the host
+  around the public `LLMEngine.generate` call: every engine step copies its
+  inputs (prompt token ids, sequence slots) from pinned host memory and reads
+  the sampled tokens back.  `roofline` is the paged-decode attention kernel, the
+  largest HBM consumer of a decode step at this shape, timed with CUDA events in
+  the same process on the engine's own KV pool.
+--workload decode: the paged-decode attention operator alone (algorithmic GB/s),
+  independent batches per GPU ("weak" scaling, no collective).
+
+`--impl reference` times the CPU path (the oracle's restatement of the
+reference's PyTorch operators inside the same harness model) on the host
+cores, on a bounded sample of the workload.
 """
 import argparse
 import json
 import os
-import subprocess
 import sys
 import threading
 import time
@@ -26,7 +39,6 @@ sys.path.insert(0, ROOT)
 
 from minivllm_b200 import synth  # noqa: E402
 
-L2_BYTES = 126 * 1024 * 1024
 # dram__bytes_read+write / algorithmic bytes of paged_decode_kernel, from the ncu capture summarised in
 # profiles/paged_decode_fp16_b64_ctx1024-4096.md (traffic grows in proportion to the KV tokens read)
 NCU_TRAFFIC_RATIO = 652.4 / 652.1
@@ -203,35 +215,6 @@ def time_cpu(run, units, min_seconds=10.0, max_iters=50):
     return units * n / dt, dt / n
 
 
-def device_timed(fn, steps, warmup, dist_on):
-    """W warm-up calls, then K calls each bracketed by CUDA events on the current stream."""
-    import torch.distributed as dist
-    for _ in range(warmup):
-        fn()
-    torch.cuda.synchronize()
-    if dist_on:
-        dist.barrier()
-    torch.cuda.synchronize()
-    evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(steps)]
-    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    t0.record()
-    for a, b in evs:
-        a.record()
-        fn()
-        b.record()
-    t1.record()
-    torch.cuda.synchronize()
-    if dist_on:
-        dist.barrier()
-    total_ms = t0.elapsed_time(t1)
-    per_call_ms = sum(a.elapsed_time(b) for a, b in evs) / steps
-    if dist_on:
-        t = torch.tensor([total_ms, per_call_ms], device="cuda", dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        total_ms, per_call_ms = float(t[0]), float(t[1])
-    return total_ms, per_call_ms
-
-
 def _time_calls(fns, iters, warmup=5):
     """Average device time (ms) of calls taken round-robin from `fns` (distinct inputs defeat L2 reuse)."""
     for i in range(warmup):
@@ -285,31 +268,216 @@ def extras(device, pk):
     nbytes = valid * 8 * (128 * (2 * 2 + 2 * 1) + 2 * 2) + 65536 * 8
     out["store_kvcache_int8"] = {"us_per_call": ms * 1e3, "GBps": nbytes / ms / 1e6,
                                  "frac_of_measured_peak": nbytes / ms / 1e6 / pk["hbm_gbs"], "bytes": nbytes}
+    del kq, vq, ks, vs, srcs, fns
+    # varlen causal prefill: 32 sequences, lengths [128,2048], 32 q / 8 kv heads, head_dim 128, bf16
+    p = synth.prefill_inputs()
+    q, k, v = (p[x].to(bf).to(device) for x in "qkv")
+    cu = p["cu_seqlens"].to(device)
+    fn = lambda: A.flash_attention_prefill(q, k, v, cu, p["scale"], 32, 8, 128)
+    ms = _time_calls([fn], 20, 5)
+    fl = synth.prefill_flops(p["lens"], 32, 128)
+    out["prefill_varlen_bf16"] = {"ms_per_call": ms, "TFLOPs": fl / ms / 1e9, "tokens": int(q.shape[0]),
+                                  "frac_of_measured_bf16_peak": fl / ms / 1e9 / pk["bf16_tflops"],
+                                  "frac_of_nominal_2250": fl / ms / 1e9 / 2250.0, "flops": fl,
+                                  "error_word": A.prefill_error_code(device)}
     return out
 
 
-def main():
-    ap = argparse.ArgumentParser()
-    ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=50)
-    ap.add_argument("--warmup", type=int, default=5)
-    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="decode", choices=["decode"])
-    ap.add_argument("--cpu-seconds", type=float, default=10.0)
-    ap.add_argument("--small", action="store_true",
-                    help="profiling case: batch 64, ctx [1024,4096] (~1.3 GB of KV), no e2e/CPU/extra legs")
-    args = ap.parse_args()
-    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
 
-    rank = int(os.environ.get("RANK", "0"))
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    local = int(os.environ.get("LOCAL_RANK", "0"))
-    metric, unit = "paged-decode attention algorithmic HBM throughput", "GB/s"
+# ----------------------------------------------------------------------------
+# engine workload
+# ----------------------------------------------------------------------------
+class EngineWorkload:
+    name = ("engine output tok/s: random-init Qwen3-8B shape (hidden 4096, 36 layers, 32q/8kv heads, head_dim 128, "
+            "intermediate 12288, vocab 151936, bf16), 512 requests, prompts uniform[512,1536] random ids, "
+            "512 greedy output tokens each, KV cache 80% of free HBM, prefill waves of 16384 tokens")
 
-    if args.impl == "reference":
-        if rank != 0:
-            return
+    def __init__(self, rank, world, device, requests=512, new_tokens=512):
+        from minivllm_b200.engine import configs
+        from minivllm_b200.engine.llm_engine import LLMEngine
+        self.rank, self.world, self.device = rank, world, device
+        self.cfg = configs.qwen3_8b_config(world_size=world)
+        self.prompts, self.sp = configs.qwen3_8b_requests(n=requests, new_tokens=new_tokens)
+        self.engine = LLMEngine(self.cfg, rank=rank, world_size=world)
+        self.out_tokens_per_step = requests * new_tokens
+        self.units_per_step = self.out_tokens_per_step
+        self.steps_run = 0
+
+    def step(self):
+        e = self.engine
+        for k in e.stats:
+            e.stats[k] = 0
+        out = e.generate(self.prompts, self.sp)
+        assert sum(len(t) for t in out["token_ids"]) == self.out_tokens_per_step
+        self.last_stats = dict(e.stats)
+        return out
+
+    # host<->device traffic of one generate(): prompt ids + per-prefill-wave metadata, per decode step the slot
+    # ids going down and the sampled tokens coming back
+    @property
+    def h2d_bytes(self):
+        s = self.last_stats
+        prompt_tokens = sum(len(p) for p in self.prompts)
+        return prompt_tokens * 8 + s["steps"] * (self.cfg["max_num_seqs"] + 1) * 4 + len(self.prompts) * 24
+
+    @property
+    def d2h_bytes(self):
+        return (self.out_tokens_per_step) * 8
+
+    def launches_per_step(self):
+        """Kernels of this library launched by one generate(): per model step and layer one store_kvcache and
+        one attention call (decode = split-K kernel + combine), plus the metadata kernels of the step."""
+        s = self.last_stats
+        layers = self.cfg["num_layers"]
+        decode_steps = self.out_tokens_per_step // len(self.prompts) - 1
+        prefill_waves = s["steps"] - decode_steps
+        return decode_steps * (layers * 3 + 1) + prefill_waves * (layers * 2 + 2)
+
+    def decode_probe(self, iters=36):
+        """Times paged_attention_decode with CUDA events on the engine's own KV pool at the shape of the
+        middle of the run: every request decoding at context = prompt + new_tokens/2, physical blocks taken
+        through a seeded permutation of the pool.  One call per layer cache, round robin, so consecutive calls
+        read different memory (each call reads far more than L2 anyway)."""
+        from minivllm_b200.layers import attention as A
+        r = self.engine.model_runner
+        c = r.model_cfg
+        H, KVH, D, bs = c.num_heads // self.world, c.num_kv_heads // self.world, c.head_dim, r.block_size
+        g = torch.Generator().manual_seed(7)
+        ctx = torch.tensor([len(p) + self.sp.max_tokens // 2 for p in self.prompts], dtype=torch.int64)
+        nblk = (ctx + bs - 1) // bs
+        assert int(nblk.sum()) <= r.num_kv_blocks
+        perm = torch.randperm(r.num_kv_blocks, generator=g)[:int(nblk.sum())].to(torch.int32)
+        bt = torch.full((len(ctx), r.max_blocks_per_seq), -1, dtype=torch.int32)
+        at = 0
+        for b, n in enumerate(nblk.tolist()):
+            bt[b, :n] = perm[at:at + n]
+            at += n
+        q = torch.randn(len(ctx), H, D, generator=g).to(r.dtype).to(self.device)
+        bt, cl = bt.to(self.device), ctx.to(self.device)
+        scale = 1.0 / D ** 0.5
+        layers = [(r.kv_cache[0, l], r.kv_cache[1, l]) for l in range(c.num_layers)]
+        fns = [lambda kc=kc, vc=vc: A.paged_attention_decode(q, kc, vc, bt, cl, scale, H, KVH, D, bs)
+               for kc, vc in layers]
+        ms = _time_calls(fns, iters, warmup=5)
+        nbytes = synth.decode_bytes(ctx, len(ctx), H, KVH, D, 2, r.max_blocks_per_seq)
+        return dict(ms=ms, bytes=nbytes, gbps=nbytes / ms / 1e6, batch=len(ctx), ctx_mean=float(ctx.float().mean()))
+
+    def close(self):
+        self.engine.exit()
+
+
+def cpu_engine_reference(requests=1, prompt_len=512, new_tokens=2, log=None):
+    """The CPU path for the engine metric on a bounded sample: the same Qwen3-8B-shaped harness (same seeded
+    weights) with every attention operator replaced by the CPU oracle (fp32), fp32 activations, weights kept
+    in bf16 and up-cast layer by layer.  Returns (output tokens per second, seconds, description)."""
+    from minivllm_b200.engine import configs
+    from minivllm_b200.engine.qwen3 import Qwen3Config, Qwen3ForCausalLM
+    from minivllm_b200.utils.context import reset_context, set_context
+    from oracle.attention_module import swap_in_oracle_attention
+    cfgd = configs.qwen3_8b_config(world_size=1)
+    mc = Qwen3Config.from_dict(cfgd)
+    build_dev = "cuda:0" if torch.cuda.is_available() else "cpu"   # weights are inputs: generate fast, then move
+    model = Qwen3ForCausalLM(mc, 0, 1, torch.bfloat16, build_dev, seed=cfgd["seed"]).to("cpu")
+    swap_in_oracle_attention(model)
+    bs = mc.block_size
+    nblk = (prompt_len + new_tokens + bs - 1) // bs
+    kv = torch.zeros(2, mc.num_layers, requests * nblk, bs, mc.num_kv_heads, mc.head_dim, dtype=torch.float32)
+    for l, layer in enumerate(model.layers):
+        layer.attn.k_cache, layer.attn.v_cache = kv[0, l], kv[1, l]
+    g = torch.Generator().manual_seed(0)
+    ids = torch.randint(0, configs.VOCAB, (requests, prompt_len), generator=g)
+    tables = torch.arange(requests * nblk, dtype=torch.int32).reshape(requests, nblk)
+
+    def slots(pos_lo, pos_hi):
+        return torch.cat([tables[r, p // bs].long() * bs + p % bs
+                          for r in range(requests) for p in [torch.arange(pos_lo, pos_hi)]])
+
+    t0 = time.perf_counter()
+    with torch.inference_mode(), torch.autocast("cpu", enabled=False):
+        import psutil
+        if psutil.virtual_memory().available > 56e9:
+            model.float()  # fp32 math on the host (the reference model is fp32-only); 33 GB of weights
+        # else: bf16 weights stay as they are and torch's CPU bf16 GEMMs are used
+        cu = torch.arange(0, (requests + 1) * prompt_len, prompt_len, dtype=torch.int32)
+        set_context(True, cu, cu, prompt_len, prompt_len, slots(0, prompt_len), None, None,
+                    positions=torch.arange(prompt_len).repeat(requests),
+                    last_token_index=(cu[1:] - 1).long())
+        tok = model.compute_logits(model(ids.reshape(-1))).argmax(-1)
+        produced = requests
+        for t in range(1, new_tokens):
+            pos = prompt_len + t - 1
+            set_context(False, None, None, 0, 0, slots(pos, pos + 1), torch.full((requests,), pos + 1), tables,
+                        positions=torch.full((requests,), pos))
+            tok = model.compute_logits(model(tok)).argmax(-1)
+            produced += requests
+        reset_context()
+    dt = time.perf_counter() - t0
+    return produced / dt, dt, (f"{requests} request(s), prompt {prompt_len}, {new_tokens} greedy output tokens, fp32 on "
+                              f"{torch.get_num_threads()} host threads (weights up-cast from bf16 inside the timed region when host RAM allows)")
+
+def device_timed(fn, steps, warmup, dist_on):
+    """W warm-up calls, then K calls each bracketed by CUDA events on the current stream; barrier and
+    synchronize on both sides; returns (device ms over the K calls, mean per-call ms, host seconds), the
+    first two as the MAX over ranks."""
+    import torch.distributed as dist
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    if dist_on:
+        dist.barrier()
+    torch.cuda.synchronize()
+    evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(steps)]
+    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    h0 = time.perf_counter()
+    t0.record()
+    for a, b in evs:
+        a.record()
+        fn()
+        b.record()
+    t1.record()
+    torch.cuda.synchronize()
+    host_s = time.perf_counter() - h0
+    if dist_on:
+        dist.barrier()
+    total_ms = t0.elapsed_time(t1)
+    per_call_ms = sum(a.elapsed_time(b) for a, b in evs) / steps
+    if dist_on:
+        t = torch.tensor([total_ms, per_call_ms, host_s], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        total_ms, per_call_ms, host_s = float(t[0]), float(t[1]), float(t[2])
+    return total_ms, per_call_ms, host_s
+
+
+def finish(line, rank):
+    """Print the line and leave without NCCL / CUDA-graph teardown (destroying a process group whose
+    collectives live in captured graphs can block)."""
+    if rank == 0:
+        print(json.dumps(line), flush=True)
+    sys.stdout.flush()
+    sys.stderr.flush()
+    os._exit(0)
+
+
+def run_reference(args, rank):
+    """CPU arm: rank 0 alone works; the other ranks exit 0."""
+    if rank != 0:
+        return
+    cores = torch.get_num_threads()
+    if args.workload == "engine":
+        metric, unit = "engine output tokens/s", "tok/s"
+        name = EngineWorkload.name
+        vals, t_all, sample = [], 0.0, ""
+        for i in range(args.warmup + args.steps):
+            v, dt, sample = cpu_engine_reference()
+            if i >= args.warmup:
+                vals.append(v)
+                t_all += dt
+        value, ms = sum(vals) / len(vals), t_all / len(vals) * 1e3
+        dtype, scaling = "f32", "strong"
+    else:
+        metric, unit = "paged-decode attention algorithmic HBM throughput", "GB/s"
         wl = DecodeWorkload(0, "cuda:0" if torch.cuda.is_available() else None)
+        name = wl.name
         run, nbytes, sample = wl.cpu_sample()
         for _ in range(args.warmup):
             run()
@@ -317,15 +485,49 @@ def main():
         for _ in range(args.steps):
             run()
         dt = time.perf_counter() - t0
-        v = nbytes * args.steps / dt / 1e9
-        line = {"impl": "reference", "metric": metric, "value": v, "unit": unit, "n_gpus": args.gpus,
-                "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3,
-                "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
-                "data": "synthetic", "config": {"workload": wl.name},
-                "cpu_baseline": {"value": v, "unit": unit, "cores": torch.get_num_threads(), "kind": "port",
-                                 "sample": sample},
-                "e2e": {"value": v, "unit": unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
-        print(json.dumps(line), flush=True)
+        value, ms = nbytes * args.steps / dt / 1e9, dt / args.steps * 1e3
+        dtype, scaling = "f32", "weak"
+    line = {"impl": "reference", "metric": metric, "value": value, "unit": unit, "n_gpus": args.gpus,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
+            "scaling": scaling, "vs_baseline": None, "dtype": dtype, "data": "synthetic",
+            "config": {"workload": name},
+            "cpu_baseline": {"value": value, "unit": unit, "cores": cores, "kind": "port", "sample": sample},
+            "e2e": {"value": value, "unit": unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=None)
+    ap.add_argument("--warmup", type=int, default=None)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="engine", choices=["engine", "decode"])
+    ap.add_argument("--cpu-seconds", type=float, default=10.0)
+    ap.add_argument("--no-extras", action="store_true", help="skip the secondary operator numbers and the CPU leg")
+    ap.add_argument("--small", action="store_true",
+                    help="decode workload only, profiling case: batch 64, ctx [1024,4096], no e2e/CPU/extra legs")
+    args = ap.parse_args()
+    ours = args.impl == "ours"
+    if args.workload == "engine":
+        # a step is a whole generate() (tens of seconds): few steps by default
+        args.steps = 2 if args.steps is None else args.steps
+        args.warmup = (3 if ours else 0) if args.warmup is None else args.warmup
+        if not ours:
+            args.steps = min(args.steps, 2)      # each CPU step is ~20-40 s of host work
+            args.warmup = min(args.warmup, 1)
+    else:
+        args.steps = 50 if args.steps is None else args.steps
+        args.warmup = 5 if args.warmup is None else args.warmup
+    if ours:
+        args.warmup = max(args.warmup, 3)
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+
+    if not ours:
+        run_reference(args, rank)
         return
 
     assert torch.cuda.is_available(), "bench.py --impl ours needs a GPU (there is no CPU path)"
@@ -337,50 +539,82 @@ def main():
         dist.init_process_group("nccl", device_id=device)
     from minivllm_b200 import _cabi
     _cabi.lib()
+    pk = peaks()
 
+    if args.workload == "engine":
+        wl = EngineWorkload(rank, world, device)
+        with ClockSampler(local, period_s=0.05) as clocks:
+            total_ms, call_ms, host_s = device_timed(wl.step, args.steps, args.warmup, dist_on)
+        value = wl.units_per_step * args.steps / (total_ms * 1e-3)
+        e2e_value = wl.units_per_step * args.steps / host_s
+        probe = wl.decode_probe()
+        s = wl.last_stats
+        line = {
+            "metric": "engine output tokens/s", "value": value, "unit": "tok/s", "n_gpus": world,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": total_ms / args.steps,
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": wl.name, "parallelism": f"tp{world}", "kv_blocks_per_gpu": wl.engine.model_runner.num_kv_blocks,
+                       "l2": "inputs larger than L2 (weights 16.4 GB and KV pool far exceed 126 MB)",
+                       "decode": "CUDA-graph replay of the whole step", "step": "one generate() over all requests"},
+            "e2e": {"value": e2e_value, "unit": "tok/s", "h2d_bytes_per_step": wl.h2d_bytes,
+                    "d2h_bytes_per_step": wl.d2h_bytes},
+            "gpu_launches": wl.launches_per_step() * args.steps,
+            "roofline": {"bound": "hbm", "achieved": probe["gbps"], "peak": pk["hbm_gbs"], "unit": "GB/s",
+                         "frac": probe["gbps"] / pk["hbm_gbs"], "traffic": probe["bytes"] * NCU_TRAFFIC_RATIO,
+                         "traffic_note": "ncu dram bytes of the batch-64 op case scaled by KV tokens",
+                         "peak_source": pk["src"], "kernel": "paged_decode_kernel (+combine)",
+                         "how": "CUDA events around the operator on the engine's KV pool, batch %d, mean ctx %.0f, "
+                                "one call per layer cache" % (probe["batch"], probe["ctx_mean"]),
+                         "ms_per_launch": probe["ms"], "frac_of_nominal_8TBs": probe["gbps"] / 8000.0},
+            "clocks": clocks.summary(),
+            "phase_split": {"prefill_s": s["prefill_s"], "decode_s": s["decode_s"], "engine_steps": s["steps"],
+                            "prefill_tokens": s["prefill_tokens"]},
+        }
+        if rank == 0 and world == 1 and not args.no_extras:
+            line["extra"] = extras(device, pk)
+            wl.close()
+            del wl
+            torch.cuda.empty_cache()
+            v, dt, sample = cpu_engine_reference()
+            line["cpu_baseline"] = {"value": v, "unit": "tok/s", "cores": torch.get_num_threads(), "kind": "port",
+                                    "sample": sample}
+        finish(line, rank)
+
+    # ---- decode operator workload ----
     if args.small:
         wl = DecodeWorkload(rank, device, batch=64, ctx_lo=1024, ctx_hi=4096)
         wl.name = wl.name.replace("batch 256, ctx uniform[1024,8192]", "batch 64, ctx uniform[1024,4096]")
     else:
         wl = DecodeWorkload(rank, device)
     with ClockSampler(local) as clocks:
-        total_ms, call_ms = device_timed(wl.step_resident, args.steps, args.warmup, dist_on)
-    if args.small:
-        e2e_total_ms = float("nan")
-    else:
-        e2e_total_ms, _ = device_timed(wl.step_e2e, args.steps, args.warmup, dist_on)
-
-    pk = peaks()
+        total_ms, call_ms, _ = device_timed(wl.step_resident, args.steps, args.warmup, dist_on)
+    e2e_total_ms = float("nan") if args.small else device_timed(wl.step_e2e, args.steps, args.warmup, dist_on)[0]
     units = wl.units_per_step * world
     value = units * args.steps / (total_ms * 1e-3) / 1e9
-    e2e_value = units * args.steps / (e2e_total_ms * 1e-3) / 1e9
     achieved = wl.bytes_per_step / (call_ms * 1e-3) / 1e9
     line = {
-        "metric": metric, "value": value, "unit": unit, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
-        "ms_per_step": total_ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-        "dtype": "f16", "data": "synthetic",
+        "metric": "paged-decode attention algorithmic HBM throughput", "value": value, "unit": "GB/s",
+        "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": total_ms / args.steps,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
         "config": {"workload": wl.name, "l2": "inputs larger than L2 (KV read per step %.2f GB)" %
                    (wl.bytes_per_step / 1e9), "sharding": "independent batches per GPU, no collective"},
-        "e2e": {"value": e2e_value, "unit": unit, "h2d_bytes_per_step": wl.h2d_bytes,
-                "d2h_bytes_per_step": wl.d2h_bytes},
+        "e2e": {"value": units * args.steps / (e2e_total_ms * 1e-3) / 1e9, "unit": "GB/s",
+                "h2d_bytes_per_step": wl.h2d_bytes, "d2h_bytes_per_step": wl.d2h_bytes},
         "gpu_launches": wl.launches_per_step * args.steps,
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": pk["hbm_gbs"], "unit": "GB/s",
                      "frac": achieved / pk["hbm_gbs"], "traffic": wl.bytes_per_step * NCU_TRAFFIC_RATIO,
-                     "traffic_note": "ncu dram bytes of the batch-64 case scaled by KV tokens", "peak_source": pk["src"],
-                     "kernel": "paged_decode_kernel (+combine)", "frac_of_nominal_8TBs": achieved / 8000.0},
+                     "traffic_note": "ncu dram bytes of the batch-64 case scaled by KV tokens",
+                     "peak_source": pk["src"], "kernel": "paged_decode_kernel (+combine)",
+                     "frac_of_nominal_8TBs": achieved / 8000.0},
         "clocks": clocks.summary(),
     }
-    if rank == 0:
-        if world == 1 and not args.small:
-            line["extra"] = extras(device, pk)
-            run, nbytes, sample = wl.cpu_sample()
-            v, _ = time_cpu(run, nbytes / 1e9, min_seconds=args.cpu_seconds)
-            line["cpu_baseline"] = {"value": v, "unit": unit, "cores": torch.get_num_threads(), "kind": "port",
-                                    "sample": sample}
-        print(json.dumps(line), flush=True)
-    if dist_on:
-        import torch.distributed as dist
-        dist.destroy_process_group()
+    if rank == 0 and world == 1 and not args.small and not args.no_extras:
+        line["extra"] = extras(device, pk)
+        run, nbytes, sample = wl.cpu_sample()
+        v, _ = time_cpu(run, nbytes / 1e9, min_seconds=args.cpu_seconds)
+        line["cpu_baseline"] = {"value": v, "unit": "GB/s", "cores": torch.get_num_threads(), "kind": "port",
+                                "sample": sample}
+    finish(line, rank)
 
 
 if __name__ == "__main__":

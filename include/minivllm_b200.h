@@ -198,6 +198,29 @@ int mv_update_block_tables(const int32_t* updates, int num_updates,
                            int32_t* tables, int64_t tables_stride,
                            int max_blocks, int num_slots, void* stream);
 
+/*
+ * Fused pre-attention step on the fused qkv projection output
+ * qkv (tokens, (num_heads + 2*num_kv_heads) * 128), token stride in elements:
+ * RMSNorm of every q and k head row (x * rsqrt(mean(x^2) + eps) * gamma,
+ * rounded to the model dtype), rotate-half rotary embedding from fp32
+ * cos/sin tables (max_position, 64) at positions[t], then q -> q_out
+ * (tokens, num_heads, 128), k -> k_out (tokens, num_kv_heads, 128) and, when
+ * slot_mapping is non-null, k and v -> the paged caches at slot_mapping[t]
+ * (negative = skip), i.e. store_kvcache fused in.
+ * Replaces, in one launch: src/myvllm/models/qwen3.py:104-108 (rms_norm of q
+ * and k, rotary_emb), layers/layernorm.py:10-17, layers/rotary_embedding.py
+ * :4-23,77-83 and the store_kvcache call of layers/attention.py:498-510.
+ */
+int mv_qk_norm_rope_store(const void* qkv, int64_t qkv_stride_tok,
+                          const int64_t* positions, const float* cos_table,
+                          const float* sin_table, int max_position,
+                          const void* gamma_q, const void* gamma_k, float eps,
+                          void* q_out, void* k_out, void* k_cache,
+                          void* v_cache, const int64_t* slot_mapping,
+                          int64_t num_slots, int64_t num_tokens, int num_heads,
+                          int num_kv_heads, int head_dim, int dtype,
+                          void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -41,6 +41,9 @@ SIGNATURES = {
     "mv_build_prefill_meta": (_c_int, [_c_ptr, _c_ptr, _c_ptr, _c_int, _c_i64, _c_ptr, _c_i64, _c_int, _c_int,
                                        _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr]),
     "mv_update_block_tables": (_c_int, [_c_ptr, _c_int, _c_ptr, _c_i64, _c_int, _c_int, _c_ptr]),
+    "mv_qk_norm_rope_store": (_c_int, [_c_ptr, _c_i64, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_ptr, _c_ptr, _c_f32,
+                                       _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_i64, _c_i64, _c_int, _c_int,
+                                       _c_int, _c_int, _c_ptr]),
 }
 
 _lib = None

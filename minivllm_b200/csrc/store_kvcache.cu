@@ -75,10 +75,10 @@ __device__ __noinline__ int quant_exact(float x, float s) {
 // (relative error 2^-23) rounds to the same integer as the quotient unless the
 // quotient is a tie.  Fast path, per element: multiply, round by adding
 // 1.5*2^23 (the code is then the low byte of the sum), and measure the
-// distance of the product from its rounded value; if any element of the
-// thread comes within 2^-10 of a half-integer, or the scale is not a normal
-// fp16 number (then |x/s| may exceed 127.5 and needs the clamp), all eight
-// elements take the exact path.  One IEEE division and one IEEE reciprocal per
+// distance of the product from its rounded value; an element that comes
+// within 1e-4 of a half-integer is redone on the exact path, and so are all
+// eight when the scale is not a normal fp16 number (then |x/s| may exceed
+// 127.5 and needs the clamp).  One IEEE division and one IEEE reciprocal per
 // head row (lane 0 of the group), none per element.
 template <typename T, int GROUP>
 __device__ __forceinline__ void quant_chunk(const uint4& raw, bool live, uint2& codes, __half& scale16) {
@@ -106,18 +106,24 @@ __device__ __forceinline__ void quant_chunk(const uint4& raw, bool live, uint2& 
   scale16 = __float2half_rn(s);  // s is an fp16 value already: exact
 
   constexpr float kMagic = 12582912.f;  // 1.5 * 2^23: adding it rounds to nearest-even integer
+  constexpr float kNearTie = 0.4999f;   // product error is < 127 * 2^-23 = 1.6e-5: anything closer to k + 1/2 is re-done
   uint32_t t[8];
-  float worst = 0.f;
+  float dist[8], worst = 0.f;
 #pragma unroll
   for (int j = 0; j < 8; ++j) {
     const float y = x[j] * inv;
     const float tj = y + kMagic;
     t[j] = __float_as_uint(tj);
-    worst = fmaxf(worst, fabsf(y - (tj - kMagic)));
+    dist[j] = fabsf(y - (tj - kMagic));
+    worst = fmaxf(worst, dist[j]);
   }
-  if (inv == 0.f || worst > 0.499f) {
+  if (inv == 0.f) {
 #pragma unroll
     for (int j = 0; j < 8; ++j) t[j] = static_cast<uint32_t>(quant_exact(x[j], s));
+  } else if (worst > kNearTie) {
+#pragma unroll
+    for (int j = 0; j < 8; ++j)
+      if (dist[j] > kNearTie) t[j] = static_cast<uint32_t>(quant_exact(x[j], s));
   }
   // low bytes of t[0..7] -> two words
   uint32_t a01, a23;

@@ -21,7 +21,7 @@ import torch
 import torch.nn as nn
 import torch.nn.functional as F
 
-from ..layers.attention import Attention
+from ..layers.attention import Attention, qk_norm_rope_store
 from ..utils.context import get_context
 
 RMS_EPS = 1e-5
@@ -41,6 +41,7 @@ class Qwen3Config:
     tie_word_embeddings: bool = True
     scale: float = 1.0
     block_size: int = 256
+    fused_pre_attention: bool = True
 
     @staticmethod
     def from_dict(c):
@@ -50,7 +51,8 @@ class Qwen3Config:
                            intermediate_size=c["intermediate_size"], rope_theta=c.get("base", 1e6),
                            max_position=c.get("max_position", c.get("max_model_length", 4096)),
                            tie_word_embeddings=c.get("tie_word_embeddings", True), scale=c.get("scale", 1.0),
-                           block_size=c.get("block_size", 256))
+                           block_size=c.get("block_size", 256),
+                           fused_pre_attention=c.get("fused_pre_attention", True))
 
 
 def _seeded_normal(shape, seed, device, std=0.02):
@@ -110,16 +112,27 @@ class DecoderLayer(nn.Module):
         ones = lambda n: nn.Parameter(torch.ones(n, dtype=dtype, device=device), requires_grad=False)
         self.input_norm_w, self.post_norm_w, self.qk_norm_w = ones(hid), ones(hid), ones(D)
         self.attn = Attention(self.h, D, cfg.scale, self.kvh, cfg.block_size)
+        # the fused kernel is CUDA-only and written for head_dim 128
+        self.fused_pre_attention = cfg.fused_pre_attention and D == 128 and torch.device(device).type == "cuda"
 
-    def forward(self, x, residual, cos, sin):
+    def forward(self, x, residual, cos, sin, rope=None):
         residual = x if residual is None else residual + x
         h = F.rms_norm(residual, (residual.shape[-1],), self.input_norm_w, RMS_EPS)
         qkv = F.linear(h, self.qkv_w)
-        q, k, v = qkv.split([self.h * self.d, self.kvh * self.d, self.kvh * self.d], dim=-1)
-        q = F.rms_norm(q.reshape(-1, self.h, self.d), (self.d,), self.qk_norm_w, RMS_EPS)
-        k = F.rms_norm(k.reshape(-1, self.kvh, self.d), (self.d,), self.qk_norm_w, RMS_EPS)
-        q, k = apply_rope(q, cos, sin), apply_rope(k, cos, sin)
-        o = self.attn(q, k, v.view(-1, self.kvh, self.d))     # v stays a strided view of qkv
+        v = qkv[:, (self.h + self.kvh) * self.d:].view(-1, self.kvh, self.d)   # v stays a strided view of qkv
+        if self.fused_pre_attention:
+            # one launch: q/k RMSNorm + RoPE + the K/V scatter into the paged cache
+            ctx = get_context()
+            a = self.attn
+            q, k = qk_norm_rope_store(qkv, ctx.positions, rope[0], rope[1], self.qk_norm_w, self.qk_norm_w, RMS_EPS,
+                                      self.h, self.kvh, self.d, a.k_cache, a.v_cache, ctx.slot_mapping)
+            o = a(q, k, v, store=False)
+        else:
+            q, k, _ = qkv.split([self.h * self.d, self.kvh * self.d, self.kvh * self.d], dim=-1)
+            q = F.rms_norm(q.reshape(-1, self.h, self.d), (self.d,), self.qk_norm_w, RMS_EPS)
+            k = F.rms_norm(k.reshape(-1, self.kvh, self.d), (self.d,), self.qk_norm_w, RMS_EPS)
+            q, k = apply_rope(q, cos, sin), apply_rope(k, cos, sin)
+            o = self.attn(q, k, v)
         o = F.linear(o, self.o_w)
         if self.tp_size > 1:
             torch.distributed.all_reduce(o)
@@ -156,10 +169,11 @@ class Qwen3ForCausalLM(nn.Module):
         positions = get_context().positions
         if positions is None:
             raise ValueError("Context.positions must be set before the model runs")
-        cos, sin = self.rope_cos[positions], self.rope_sin[positions]
+        fused = all(l.fused_pre_attention for l in self.layers)
+        cos, sin = (None, None) if fused else (self.rope_cos[positions], self.rope_sin[positions])
         x, residual = F.embedding(input_ids, self.embed), None
         for layer in self.layers:
-            x, residual = layer(x, residual, cos, sin)
+            x, residual = layer(x, residual, cos, sin, (self.rope_cos, self.rope_sin))
         return F.rms_norm(residual + x, (x.shape[-1],), self.final_norm_w, RMS_EPS)
 
     def compute_logits(self, hidden):

@@ -200,6 +200,45 @@ def flash_attention_prefill(q, k, v, cu_seqlens, scale, num_heads, num_kv_heads,
     return out
 
 
+def qk_norm_rope_store(qkv, positions, cos_table, sin_table, gamma_q, gamma_k, eps, num_heads, num_kv_heads,
+                       head_dim, k_cache=None, v_cache=None, slot_mapping=None):
+    """One launch for what the reference does in a dozen before attention: RMSNorm of the q and k heads,
+    rotary embedding, and the scatter of k and v into the paged cache.
+
+    qkv (tokens, (heads + 2*kv_heads) * head_dim) is the fused projection output (any token stride);
+    positions (tokens,) int64; cos_table / sin_table (max_position, head_dim/2) fp32.
+    Returns (q, k) as new contiguous (tokens, heads, head_dim) / (tokens, kv_heads, head_dim) tensors; v is
+    still `qkv[..., -kv_heads*head_dim:]`.  With caches and a slot_mapping, k and v are also stored.
+    Reference: src/myvllm/models/qwen3.py:104-108 and src/myvllm/layers/attention.py:498-510.
+    """
+    _cabi.require_cuda(qkv, positions, cos_table, sin_table, gamma_q, gamma_k)
+    tokens = qkv.shape[0]
+    width = (num_heads + 2 * num_kv_heads) * head_dim
+    if qkv.dim() != 2 or qkv.shape[1] != width or qkv.stride(1) != 1:
+        raise ValueError(f"qkv must be (tokens, {width}) with dense rows")
+    if positions.dtype != torch.int64 or positions.numel() != tokens or not positions.is_contiguous():
+        raise ValueError("positions must be a contiguous int64 vector with one entry per token")
+    for t in (cos_table, sin_table):
+        if t.dtype != torch.float32 or t.dim() != 2 or t.shape[1] != head_dim // 2 or not t.is_contiguous():
+            raise ValueError("cos/sin tables must be contiguous fp32 (max_position, head_dim/2)")
+    q = torch.empty((tokens, num_heads, head_dim), dtype=qkv.dtype, device=qkv.device)
+    k = torch.empty((tokens, num_kv_heads, head_dim), dtype=qkv.dtype, device=qkv.device)
+    store = slot_mapping is not None and k_cache is not None and k_cache.numel() > 0
+    if store:
+        if k_cache.dtype != qkv.dtype or v_cache.dtype != qkv.dtype or tuple(k_cache.shape[2:]) != (num_kv_heads, head_dim):
+            raise ValueError("fused store needs fp16/bf16 caches of shape (blocks, block_size, kv_heads, head_dim)")
+        if slot_mapping.dtype != torch.int64 or slot_mapping.numel() != tokens:
+            raise ValueError("slot_mapping must be int64 with one entry per token")
+    rc = _cabi.lib().mv_qk_norm_rope_store(
+        qkv.data_ptr(), qkv.stride(0) if tokens > 1 else width, positions.data_ptr(), cos_table.data_ptr(),
+        sin_table.data_ptr(), cos_table.shape[0], gamma_q.data_ptr(), gamma_k.data_ptr(), float(eps), q.data_ptr(),
+        k.data_ptr(), k_cache.data_ptr() if store else None, v_cache.data_ptr() if store else None,
+        slot_mapping.data_ptr() if store else None, k_cache.shape[0] * k_cache.shape[1] if store else 0, tokens,
+        num_heads, num_kv_heads, head_dim, _cabi.dtype_code(qkv.dtype), _cabi.stream_ptr())
+    _cabi.check(rc)
+    return q, k
+
+
 class Attention(nn.Module):
     """Attention layer of the engine: stores the step's K/V into the paged cache
     and runs varlen prefill or paged decode, as told by the global Context.
@@ -224,7 +263,8 @@ class Attention(nn.Module):
         self.k_cache = self.v_cache = torch.tensor([])
         self.k_scale = self.v_scale = None
 
-    def forward(self, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor) -> torch.Tensor:
+    def forward(self, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, store: bool = True) -> torch.Tensor:
+        """`store=False` when the caller already wrote this step's K/V into the cache (qk_norm_rope_store)."""
         ctx = get_context()
         k_cache, v_cache = self.k_cache, self.v_cache
         if q.dim() == 4:  # (B, N, heads, head_dim) -> packed tokens; decode passes N == 1
@@ -232,7 +272,7 @@ class Attention(nn.Module):
             k = k.reshape(-1, k.shape[-2], k.shape[-1])
             v = v.reshape(-1, v.shape[-2], v.shape[-1])
         has_cache = k_cache.numel() > 0 and v_cache.numel() > 0
-        if has_cache and ctx.slot_mapping is not None:
+        if store and has_cache and ctx.slot_mapping is not None:
             store_kvcache(k, v, k_cache, v_cache, ctx.slot_mapping, k_cache.shape[1],
                           k_scale=self.k_scale, v_scale=self.v_scale)
         scale = self.scale / (self.head_dim ** 0.5)

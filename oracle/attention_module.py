@@ -17,7 +17,7 @@ class OracleAttention(nn.Module):
         self.block_size = block_size
         self.k_cache = self.v_cache = torch.tensor([])
 
-    def forward(self, q, k, v):
+    def forward(self, q, k, v, store=True):
         ctx = get_context()
         dev, dt = q.device, q.dtype
         kc, vc = self.k_cache, self.v_cache
@@ -44,4 +44,5 @@ def swap_in_oracle_attention(model):
         o = OracleAttention(a.num_heads, a.head_dim, a.scale, a.num_kv_heads, a.block_size)
         o.k_cache, o.v_cache = a.k_cache, a.v_cache
         layer.attn = o
+        layer.fused_pre_attention = False   # the reference path: separate norm, RoPE and store
     return model

@@ -150,3 +150,19 @@ def flash_attention_prefill(q, k, v, cu_seqlens, scale, num_heads, num_kv_heads,
         o = torch.einsum("kgij,jkd->ikgd", probs, vf[a:e])
         out[a:e] = o.reshape(n, num_heads, head_dim)
     return out
+
+
+# --------------------------------------------------------------------------
+# q/k RMSNorm + rotary embedding (the step right before the attention operators)
+# --------------------------------------------------------------------------
+def qk_norm_rope(x, positions, cos_table, sin_table, gamma, eps, dtype):
+    """x (tokens, heads, head_dim) already rounded to `dtype`; fp32 restatement of
+    src/myvllm/layers/layernorm.py:10-17 (x / sqrt(mean(x^2) + eps) * gamma) followed by
+    src/myvllm/layers/rotary_embedding.py:4-23 (rotate-half with cos/sin[positions]), with the result of
+    each of the two steps rounded to the model dtype, as two separate kernels in that dtype would."""
+    xf = x.to(torch.float32)
+    n = xf / torch.sqrt(xf.pow(2).mean(-1, keepdim=True) + eps) * gamma.to(torch.float32)
+    n = n.to(dtype).to(torch.float32)
+    cos, sin = cos_table[positions][:, None, :], sin_table[positions][:, None, :]
+    x1, x2 = n.chunk(2, dim=-1)
+    return torch.cat([x1 * cos - x2 * sin, x1 * sin + x2 * cos], dim=-1).to(dtype)

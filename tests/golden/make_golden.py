@@ -155,7 +155,32 @@ def metadata_main():
         mr.torch.tensor = real_tensor
 
 
+
+
+def prenorm_main():
+    """q/k RMSNorm + rotary embedding through the reference's own LayerNorm and RotaryEmbedding (fp32, CPU)."""
+    from myvllm.layers.layernorm import LayerNorm
+    from myvllm.layers.rotary_embedding import RotaryEmbedding
+    g = torch.Generator().manual_seed(40)
+    tokens, heads, kv_heads, d = 37, 4, 2, 128
+    q = torch.randn(tokens, heads, d, generator=g)
+    k = torch.randn(tokens, kv_heads, d, generator=g) * 3
+    gamma = torch.rand(d, generator=g) + 0.5
+    positions = torch.randint(0, 500, (tokens,), generator=g)
+    norm = LayerNorm(gamma)                      # eps defaults to 1e-5, as in the engine
+    rope = RotaryEmbedding(base=1000000, rotary_embedding=d, max_position=512)
+    qo, ko = rope(positions, norm(q), norm(k))
+    np.savez_compressed(os.path.join(HERE, "prenorm_rope.npz"), q=qo.numpy(), k=ko.numpy(), seed=40,
+                        shape=np.array([tokens, heads, kv_heads, d]))
+    print("prenorm_rope", qo.shape, ko.shape)
+
+
 if __name__ == "__main__":
-    if "--metadata-only" not in sys.argv:
+    only = [a for a in sys.argv[1:] if a.startswith("--only=")]
+    which = only[0].split("=")[1].split(",") if only else ["ops", "metadata", "prenorm"]
+    if "ops" in which:
         main()
-    metadata_main()
+    if "metadata" in which:
+        metadata_main()
+    if "prenorm" in which:
+        prenorm_main()

@@ -6,7 +6,7 @@ import torch
 
 from minivllm_b200.engine.llm_engine import LLMEngine
 from minivllm_b200.engine.sequence import SamplingParams
-from tests.oracle_attention_module import swap_in_oracle_attention
+from oracle.attention_module import swap_in_oracle_attention
 
 pytestmark = pytest.mark.gpu
 

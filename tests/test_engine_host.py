@@ -77,7 +77,7 @@ import os, sys, torch, torch.distributed as dist
 sys.path.insert(0, os.environ["MV_ROOT"])
 from minivllm_b200.engine.qwen3 import Qwen3Config, Qwen3ForCausalLM
 from minivllm_b200.utils.context import set_context
-from tests.oracle_attention_module import swap_in_oracle_attention
+from oracle.attention_module import swap_in_oracle_attention
 rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
 dist.init_process_group("gloo", rank=rank, world_size=world)
 cfg = Qwen3Config(vocab_size=97, hidden_size=64, num_layers=2, num_heads=4, num_kv_heads=2, head_dim=16,
