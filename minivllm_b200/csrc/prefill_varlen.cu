@@ -11,7 +11,7 @@
 //   warps 0-3   softmax of head A: thread i owns row i (= TMEM lane i)
 //   warps 4-7   softmax of head B
 //   warp  8     TMA producer: Q once, then K and V tiles through 2-stage rings
-//   warp  9     MMA issuer: one thread issues tcgen05.mma, commits to mbarriers
+//   warp  9     MMA issuer: one thread issues every tcgen05.mma and commits to mbarriers
 // Tensor memory (512 columns): S_A | S_B | O_A | O_B, 128 fp32 columns each.
 // S = Q K^T is an SS MMA (both operands in 128B-swizzled shared memory, written
 // by TMA); the softmax warps read S with tcgen05.ld, write P (bf16/fp16, packed
@@ -37,6 +37,10 @@ constexpr int kPfHalfBytes = kPfTile * 128;                 // one 64-element ha
 constexpr int kPfTileBytes = 2 * kPfHalfBytes;              // 32 KB
 constexpr int kPfStages = 2;
 constexpr int kPfSmemBytes = 2 * kPfTileBytes + 2 * kPfStages * kPfTileBytes + 1024;  // Q(2 heads) + K ring + V ring + align
+// Which of the 32 score pairs of a half row take the polynomial exp2 (the others use the special-function unit).
+#ifndef MV_PF_POLY_PRED
+#define MV_PF_POLY_PRED(i) (((i) & 3) == 3)   // a quarter: measured best of 0, 1/4, 1/2, 3/4, all
+#endif
 constexpr float kRescaleThreshold = 8.f;                    // log2 units
 
 struct PrefillParams {
@@ -51,6 +55,20 @@ struct PrefillParams {
 
 enum { BAR_Q = 0, BAR_KFULL = 1, BAR_KEMPTY = 3, BAR_VFULL = 5, BAR_VEMPTY = 7, BAR_SFULL = 9, BAR_PREADY = 11,
        BAR_ODONE = 13, BAR_COUNT = 15 };
+
+#ifdef MV_PF_TRACE
+// Timeline probe (debug builds only, -DMV_PF_TRACE): one thread of each role of ONE CTA writes clock64()
+// stamps per KV step, so that the phases of the pipeline can be read off without a profiler.
+__device__ long long* g_pf_trace = nullptr;
+__device__ int g_pf_trace_cta = -1;
+#define PF_STAMP(role, j, k)                                                                           \
+  do {                                                                                                 \
+    if (g_pf_trace && static_cast<int>(blockIdx.x) == g_pf_trace_cta && blockIdx.y == 0 && (j) < 32)  \
+      g_pf_trace[((role) * 32 + (j)) * 8 + (k)] = clock64();                                          \
+  } while (0)
+#else
+#define PF_STAMP(role, j, k) do {} while (0)
+#endif
 
 __device__ __forceinline__ float ex2(float x) {
   float y;
@@ -190,37 +208,52 @@ prefill_varlen_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
       }
     } else if (warp == 9) {
       // ------------------------------- MMA issuer -------------------------------
-      if (lane == 0) {
+      // ONE warp, converged, issues every MMA of the CTA through its elected lane.  (Issuing the two heads from two
+      // warps was measured: the tensor pipe then serialises, ~1000 cycles per MMA.)
+      // A single thread cannot hide the latency of its own instruction stream, so
+      // the descriptors are reduced to one add per operand: the fixed part is
+      // built once, offsets are compile-time constants in 16-byte units.
+      {
         const uint32_t idesc_qk = tc::instr_desc_f16(p.fmt, p.fmt, false, 128, 128);
         // A and B must have the same format: fp16 P against bf16 V is rejected
         // by the hardware as an illegal instruction.
         const uint32_t idesc_pv = tc::instr_desc_f16(p.fmt, p.fmt, true, 128, 128);
         const int nt = has_b ? 2 : 1;
+        const uint32_t desc_hi = tc::kDescHiSw128Sbo1024;
+        const uint32_t q_lo0 = tc::desc_lo(q_smem, 16);
+        const uint32_t k_lo0 = tc::desc_lo(k_smem, 16);
+        const uint32_t v_lo0 = tc::desc_lo(v_smem, kPfHalfBytes);
         auto issue_qk = [&](int t, int s) {
+          const uint32_t q_lo = q_lo0 + t * (kPfTileBytes >> 4);
+          const uint32_t k_lo = k_lo0 + s * (kPfTileBytes >> 4);
+          const uint32_t s_tmem = tmem + t * 128;
 #pragma unroll
           for (int h = 0; h < 2; ++h)
 #pragma unroll
             for (int ks = 0; ks < 4; ++ks) {
-              const uint64_t a = tc::smem_desc_sw128(q_smem + t * kPfTileBytes + h * kPfHalfBytes + ks * 32, 16, 1024);
-              const uint64_t b = tc::smem_desc_sw128(k_smem + s * kPfTileBytes + h * kPfHalfBytes + ks * 32, 16, 1024);
-              tc::mma_ss(tmem + t * 128, a, b, idesc_qk, (h | ks) != 0);
+              const uint32_t off = (h * kPfHalfBytes + ks * 32) >> 4;
+              if (tc::elect_one())
+                tc::mma_ss(s_tmem, tc::desc64(q_lo + off, desc_hi), tc::desc64(k_lo + off, desc_hi), idesc_qk,
+                           (h | ks) != 0);
             }
         };
         auto issue_pv = [&](int t, int s, bool accum, int p_col) {
+          const uint32_t v_lo = v_lo0 + s * (kPfTileBytes >> 4);
+          const uint32_t p_tmem = tmem + t * 128 + p_col, o_tmem = tmem + 256 + t * 128;
 #pragma unroll
-          for (int ks = 0; ks < 8; ++ks) {
-            const uint64_t b = tc::smem_desc_sw128(v_smem + s * kPfTileBytes + ks * 2048, kPfHalfBytes, 1024);
-            tc::mma_ts(tmem + 256 + t * 128, tmem + t * 128 + p_col + ks * 8, b, idesc_pv, accum || ks != 0);
-          }
+          for (int ks = 0; ks < 8; ++ks)
+            if (tc::elect_one())
+              tc::mma_ts(o_tmem, p_tmem + ks * 8, tc::desc64(v_lo + ks * (2048 >> 4), desc_hi), idesc_pv,
+                         accum || ks != 0);
         };
         tc::mbar_wait(bar(BAR_Q), 0, abort_flag, p.error_word, 3);
         tc::mbar_wait(bar(BAR_KFULL + 0), 0, abort_flag, p.error_word, 4);
         tc::fence_after_sync();
         for (int t = 0; t < nt; ++t) {
           issue_qk(t, 0);
-          tc::mma_commit(bar(BAR_SFULL + t));
+          if (tc::elect_one()) tc::mma_commit(bar(BAR_SFULL + t));
         }
-        tc::mma_commit(bar(BAR_KEMPTY + 0));  // K stage 0 is free once QK(0) of both heads has run
+        if (tc::elect_one()) tc::mma_commit(bar(BAR_KEMPTY + 0));  // K stage 0 is free once QK(0) of both heads has run
         for (int j = 0; j < n_kv; ++j) {
           const int s = j % kPfStages;
           const uint32_t ph = (j / kPfStages) & 1;
@@ -231,16 +264,27 @@ prefill_varlen_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
           for (int t = 0; t < nt; ++t) {
             tc::mbar_wait(bar(BAR_PREADY + t), j & 1, abort_flag, p.error_word, 7);
             tc::fence_after_sync();
+            if (lane == 0) PF_STAMP(2 + t, j, 0);
             issue_pv(t, s, j > 0, 0);
             if (split_p) issue_pv(t, s, true, 64);   // residue of P, see the softmax warps
-            tc::mma_commit(bar(BAR_ODONE + t));
+            if (tc::elect_one()) tc::mma_commit(bar(BAR_ODONE + t));
+            if (lane == 0) PF_STAMP(2 + t, j, 1);
+#ifdef MV_PF_TRACE_SERIAL
+            tc::mbar_wait(bar(BAR_ODONE + t), j & 1, abort_flag, p.error_word, 11);   // probe: PV alone, issue to completion
+            if (lane == 0) PF_STAMP(2 + t, j, 3);
+#endif
             if (more) {
               issue_qk(t, s1);
-              tc::mma_commit(bar(BAR_SFULL + t));
+              if (tc::elect_one()) tc::mma_commit(bar(BAR_SFULL + t));
             }
+            if (lane == 0) PF_STAMP(2 + t, j, 2);
+#ifdef MV_PF_TRACE_SERIAL
+            if (more) tc::mbar_wait(bar(BAR_SFULL + t), (j + 1) & 1, abort_flag, p.error_word, 12);  // probe: QK alone
+            if (lane == 0) PF_STAMP(2 + t, j, 4);
+#endif
           }
-          tc::mma_commit(bar(BAR_VEMPTY + s));     // both PV(j) done -> V stage free
-          if (more) tc::mma_commit(bar(BAR_KEMPTY + s1));               // QK(j+1) of both heads issued
+          if (tc::elect_one()) tc::mma_commit(bar(BAR_VEMPTY + s));     // both PV(j) issued -> V stage free when they have run
+          if (more) if (tc::elect_one()) tc::mma_commit(bar(BAR_KEMPTY + s1));
         }
       }
     }
@@ -274,6 +318,8 @@ prefill_varlen_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
       for (int j = 0; j < n_kv; ++j) {
         tc::mbar_wait(bar(BAR_SFULL + t), j & 1, abort_flag, p.error_word, 8);
         tc::fence_after_sync();
+        if (tid == 0) PF_STAMP(0, j, 0);
+        if (tid == 128) PF_STAMP(1, j, 0);
         const bool diag = j == n_kv - 1;
         float sum = 0.f;
         if (!split_p) {
@@ -282,6 +328,7 @@ prefill_varlen_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
 #pragma unroll
           for (int c = 0; c < 4; ++c) tc::tmem_ld32(s_addr + c * 32, sv[c]);
           tc::wait_ld();
+          if (tid == 0) PF_STAMP(0, j, 1);
           if (diag) {
 #pragma unroll
             for (int c = 0; c < 4; ++c)
@@ -289,28 +336,47 @@ prefill_varlen_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
               for (int i = 0; i < 32; ++i)
                 if (c * 32 + i > row) sv[c][i] = 0xff800000u;  // -inf
           }
-          float mx = -INFINITY;
+          // Row maximum: three-input max, eight independent chains (one chain of 128 dependent ops costs ~500 cycles).
+          float mxs[8];
+#pragma unroll
+          for (int i = 0; i < 8; ++i) mxs[i] = -INFINITY;
 #pragma unroll
           for (int c = 0; c < 4; ++c)
 #pragma unroll
-            for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(sv[c][i]));
+            for (int i = 0; i < 16; ++i)
+              mxs[i & 7] = tc::max3(mxs[i & 7], __uint_as_float(sv[c][2 * i]), __uint_as_float(sv[c][2 * i + 1]));
+          float mx = fmaxf(tc::max3(mxs[0], mxs[1], mxs[2]), tc::max3(mxs[3], mxs[4], mxs[5]));
+          mx = tc::max3(mx, mxs[6], mxs[7]);
           mx *= p.scale_log2;  // scale > 0, so max commutes with it
           const bool grow = mx > m_used + kRescaleThreshold;
           if (j > 0 && __any_sync(0xffffffffu, grow)) rescale_o(grow ? ex2(m_used - mx) : 1.f, j, l);
           if (grow) m_used = mx;
+          if (tid == 0) PF_STAMP(0, j, 2);
+          // exp2(s * scale - m) on packed pairs; a share of the pairs goes to the FMA-pipe polynomial so that
+          // the special-function unit (the slowest pipe of the tile) does not see every exponential
+          const float2 sc2 = make_float2(p.scale_log2, p.scale_log2), nm2 = make_float2(-m_used, -m_used);
+          float2 sums[4] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f), make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
 #pragma unroll
           for (int c2 = 0; c2 < 2; ++c2) {
             uint32_t pk[32];
 #pragma unroll
             for (int i = 0; i < 32; ++i) {
               const int c = 2 * c2 + (i >> 4), k = (i & 15) * 2;
-              const float p0 = ex2(fmaf(__uint_as_float(sv[c][k]), p.scale_log2, -m_used));
-              const float p1 = ex2(fmaf(__uint_as_float(sv[c][k + 1]), p.scale_log2, -m_used));
-              sum += p0 + p1;
-              pk[i] = pack2<T>(p0, p1);
+              const float2 x = tc::fma2(make_float2(__uint_as_float(sv[c][k]), __uint_as_float(sv[c][k + 1])), sc2, nm2);
+              float2 e;
+              if (MV_PF_POLY_PRED(i)) {
+                e = tc::ex2_poly2(x);
+              } else {
+                e.x = tc::ex2_mufu(x.x);
+                e.y = tc::ex2_mufu(x.y);
+              }
+              sums[i & 3] = tc::add2(sums[i & 3], e);
+              pk[i] = pack2<T>(e.x, e.y);
             }
             tc::tmem_st32(s_addr + c2 * 32, pk);   // P over the first 64 columns of S (all of S is in registers)
           }
+          const float2 s01 = tc::add2(sums[0], sums[1]), s23 = tc::add2(sums[2], sums[3]);
+          sum = (s01.x + s01.y) + (s23.x + s23.y);
         } else {
           // ---- first query tile in bf16: two passes over S, P plus its rounding residue ----
           float mx = -INFINITY;
@@ -352,9 +418,12 @@ prefill_varlen_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
           tc::tmem_st32(s_addr + 96, plo);
         }
         l += sum;
+        if (tid == 0) PF_STAMP(0, j, 3);
         tc::wait_st();
         tc::fence_before_sync();
         tc::mbar_arrive(bar(BAR_PREADY + t));
+        if (tid == 0) PF_STAMP(0, j, 4);
+        if (tid == 128) PF_STAMP(1, j, 4);
       }
       // ---- epilogue: O / l -> global ----
       tc::mbar_wait(bar(BAR_ODONE + t), (n_kv - 1) & 1, abort_flag, p.error_word, 10);
@@ -427,6 +496,14 @@ static int make_tmap(CUtensorMap* m, const void* base, int64_t tokens, int heads
 }
 
 }  // namespace mv
+
+#ifdef MV_PF_TRACE
+extern "C" int mv_debug_prefill_trace(long long* buffer, int cta) {
+  cudaMemcpyToSymbol(mv::g_pf_trace, &buffer, sizeof(buffer));
+  cudaMemcpyToSymbol(mv::g_pf_trace_cta, &cta, sizeof(cta));
+  return 0;
+}
+#endif
 
 extern "C" int mv_prefill_varlen(void* out, const void* q, const void* k, const void* v, int64_t q_stride_tok,
                                  int64_t k_stride_tok, int64_t v_stride_tok, const int32_t* cu_seqlens, int num_seqs,

@@ -129,6 +129,16 @@ __device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t saddr, uint32_t lbo
   d |= 2ull << 61;
   return d;
 }
+// The same descriptor split into its two 32-bit words, so that an issuing thread builds the fixed part once
+// and only adds offsets (16-byte units, no carry out of the 14-bit field) to the low word.
+constexpr uint32_t kDescHiSw128Sbo1024 = (1024u >> 4) | (1u << 14) | (2u << 29);
+__device__ __forceinline__ uint32_t desc_lo(uint32_t saddr, uint32_t lbo_bytes) {
+  return ((saddr & 0x3ffffu) >> 4) | (((lbo_bytes >> 4) & 0x3fffu) << 16);
+}
+__device__ __forceinline__ uint64_t desc64(uint32_t lo, uint32_t hi) {
+  return (static_cast<uint64_t>(hi) << 32) | lo;
+}
+
 // Instruction descriptor of tcgen05.mma.kind::f16: fp32 accumulate, A and B
 // formats given separately (0 = fp16, 1 = bf16), A K-major, B K-major or
 // MN-major, M x N tile.
@@ -140,6 +150,19 @@ __host__ __device__ constexpr uint32_t instr_desc_f16(uint32_t fmt_a, uint32_t f
          | ((b_mn_major ? 1u : 0u) << 16)
          | ((n >> 3) << 17) | ((m >> 4) << 24);
 }
+// One lane of a converged warp.  The MMA issuer runs its whole loop with all 32 lanes converged and lets the
+// elected lane execute the tcgen05 instructions: their operands travel through the uniform datapath, and a
+// warp that has diverged on `lane == 0` pays ~90-140 cycles per MMA to get them there (measured).
+__device__ __forceinline__ bool elect_one() {
+  uint32_t is_leader;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "elect.sync _|p, 0xffffffff;\n\t"
+      "selp.b32 %0, 1, 0, p;\n\t}"
+      : "=r"(is_leader));
+  return is_leader != 0;
+}
+
 // D[tmem] (+)= A[smem] * B[smem]
 __device__ __forceinline__ void mma_ss(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, bool accum) {
   const uint32_t acc = accum ? 1u : 0u;
@@ -159,6 +182,51 @@ __device__ __forceinline__ void mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_
 // The mbarrier gets one arrival when every MMA issued so far by this thread has completed.
 __device__ __forceinline__ void mma_commit(uint32_t bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+
+// ------------------------------------------------------- softmax arithmetic ---
+// Blackwell packed fp32 pairs (one issue slot for two lanes of work) and the three-input max.
+__device__ __forceinline__ float2 fma2(float2 a, float2 b, float2 c) {
+  float2 d;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;"
+      : "=l"(reinterpret_cast<unsigned long long&>(d))
+      : "l"(reinterpret_cast<unsigned long long&>(a)), "l"(reinterpret_cast<unsigned long long&>(b)),
+        "l"(reinterpret_cast<unsigned long long&>(c)));
+  return d;
+}
+__device__ __forceinline__ float2 add2(float2 a, float2 b) {
+  float2 d;
+  asm("add.rn.f32x2 %0, %1, %2;"
+      : "=l"(reinterpret_cast<unsigned long long&>(d))
+      : "l"(reinterpret_cast<unsigned long long&>(a)), "l"(reinterpret_cast<unsigned long long&>(b)));
+  return d;
+}
+__device__ __forceinline__ float max3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
+__device__ __forceinline__ float ex2_mufu(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+// 2^x for a pair on the FMA pipe instead of the 16-per-clock special-function unit:
+// round to the nearest integer n by adding 1.5*2^23, a degree-4 polynomial for 2^f on
+// f = x - n in [-1/2, 1/2] (relative error 4e-5, well inside the 2^-9 / 2^-11 rounding of P),
+// and n added into the exponent field.  x <= -127 gives exactly 0; x must be below 128.
+__device__ __forceinline__ float2 ex2_poly2(float2 x) {
+  const float kMagic = 12582912.f;
+  x.x = fmaxf(x.x, -127.f);
+  x.y = fmaxf(x.y, -127.f);
+  const float2 t = add2(x, make_float2(kMagic, kMagic));
+  const float2 f = add2(x, add2(make_float2(kMagic, kMagic), make_float2(-t.x, -t.y)));   // x - (t - magic)
+  float2 p = fma2(f, make_float2(0.0096181291f, 0.0096181291f), make_float2(0.0555041087f, 0.0555041087f));
+  p = fma2(p, f, make_float2(0.2402265070f, 0.2402265070f));
+  p = fma2(p, f, make_float2(0.6931471806f, 0.6931471806f));
+  p = fma2(p, f, make_float2(1.f, 1.f));
+  return make_float2(__uint_as_float(__float_as_uint(p.x) + (__float_as_uint(t.x) << 23)),
+                     __uint_as_float(__float_as_uint(p.y) + (__float_as_uint(t.y) << 23)));
 }
 
 // Register re-partitioning between warpgroups (all four warps of a warpgroup execute it).
