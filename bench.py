@@ -292,11 +292,11 @@ class EngineWorkload:
             "intermediate 12288, vocab 151936, bf16), 512 requests, prompts uniform[512,1536] random ids, "
             "512 greedy output tokens each, KV cache 80% of free HBM, prefill waves of 16384 tokens")
 
-    def __init__(self, rank, world, device, requests=512, new_tokens=512):
+    def __init__(self, rank, world, device, requests=512, new_tokens=512, **cfg_over):
         from minivllm_b200.engine import configs
         from minivllm_b200.engine.llm_engine import LLMEngine
         self.rank, self.world, self.device = rank, world, device
-        self.cfg = configs.qwen3_8b_config(world_size=world)
+        self.cfg = configs.qwen3_8b_config(world_size=world, **cfg_over)
         self.prompts, self.sp = configs.qwen3_8b_requests(n=requests, new_tokens=new_tokens)
         self.engine = LLMEngine(self.cfg, rank=rank, world_size=world)
         self.out_tokens_per_step = requests * new_tokens
@@ -506,7 +506,8 @@ def main():
     ap.add_argument("--cpu-seconds", type=float, default=10.0)
     ap.add_argument("--no-extras", action="store_true", help="skip the secondary operator numbers and the CPU leg")
     ap.add_argument("--small", action="store_true",
-                    help="decode workload only, profiling case: batch 64, ctx [1024,4096], no e2e/CPU/extra legs")
+                    help="profiling case: decode workload batch 64, ctx [1024,4096]; engine workload 32 requests x 8 "
+                         "tokens with eager decode; no e2e/CPU/extra legs")
     args = ap.parse_args()
     ours = args.impl == "ours"
     if args.workload == "engine":
@@ -541,6 +542,14 @@ def main():
     _cabi.lib()
     pk = peaks()
 
+    if args.workload == "engine" and args.small:
+        # profiling case: same model and kernels, 32 requests x 8 tokens, eager decode (a launch list of a
+        # graph-capturing run would be dominated by the 36 captures)
+        wl = EngineWorkload(rank, world, device, requests=32, new_tokens=8, enforce_eager=True, num_kv_blocks=512)
+        total_ms, call_ms, host_s = device_timed(wl.step, 1, 1, dist_on)
+        finish({"metric": "engine output tokens/s", "value": wl.units_per_step / (total_ms * 1e-3), "unit": "tok/s",
+                "n_gpus": world, "steps": 1, "warmup": 1, "config": {"workload": "profiling case: 32 requests x 8 "
+                "tokens of the engine workload, eager decode"}}, rank)
     if args.workload == "engine":
         wl = EngineWorkload(rank, world, device)
         with ClockSampler(local, period_s=0.05) as clocks:
