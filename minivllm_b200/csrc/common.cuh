@@ -50,6 +50,14 @@ __device__ __forceinline__ void st_global8(void* p, const uint2& v) {
   asm volatile("st.global.v2.u32 [%0], {%1,%2};" ::"l"(p), "r"(v.x), "r"(v.y) : "memory");
 }
 
+// 2^x on the special-function unit (2 ulp, flushes denormals): exp2f() adds range handling that the
+// attention kernels do not need (their arguments are <= 0 or -inf).
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));
 }

@@ -185,13 +185,13 @@ paged_decode_kernel(const DecodeParams p) {
       mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
       mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
       const float mn0 = fmaxf(m0, mx0), mn1 = fmaxf(m1, mx1);
-      const float a0 = exp2f(m0 - mn0), a1 = exp2f(m1 - mn1);
+      const float a0 = fast_exp2(m0 - mn0), a1 = fast_exp2(m1 - mn1);
       m0 = mn0; m1 = mn1;
       float ps0 = 0.f, ps1 = 0.f;
 #pragma unroll
       for (int n = 0; n < 2; ++n) {
-        s[n][0] = exp2f(s[n][0] - mn0); s[n][1] = exp2f(s[n][1] - mn0);
-        s[n][2] = exp2f(s[n][2] - mn1); s[n][3] = exp2f(s[n][3] - mn1);
+        s[n][0] = fast_exp2(s[n][0] - mn0); s[n][1] = fast_exp2(s[n][1] - mn0);
+        s[n][2] = fast_exp2(s[n][2] - mn1); s[n][3] = fast_exp2(s[n][3] - mn1);
         ps0 += s[n][0] + s[n][1];
         ps1 += s[n][2] + s[n][3];
       }
@@ -216,6 +216,11 @@ paged_decode_kernel(const DecodeParams p) {
           }
         }
       }
+      // the running maximum rarely moves after the first tiles: rescale only when some row of the warp needs it
+      if (__any_sync(0xffffffffu, a0 != 1.f || a1 != 1.f)) {
+#pragma unroll
+        for (int j = 0; j < NT; ++j) { o[j][0] *= a0; o[j][1] *= a0; o[j][2] *= a1; o[j][3] *= a1; }
+      }
       {
         const int row = (lane & 7) + (((lane >> 3) & 1) << 3);
         const int csel = lane >> 4;
@@ -223,10 +228,6 @@ paged_decode_kernel(const DecodeParams p) {
         for (int jp = 0; jp < KSTEPS; ++jp) {
           uint32_t vb[4];
           ldmatrix_x4_trans(vb, vbase + row * S::kRowBytes + (((2 * jp + csel) ^ (row & 7)) << 4));
-          float* oa = o[2 * jp];
-          float* ob = o[2 * jp + 1];
-          oa[0] *= a0; oa[1] *= a0; oa[2] *= a1; oa[3] *= a1;
-          ob[0] *= a0; ob[1] *= a0; ob[2] *= a1; ob[3] *= a1;
           Mma16816<T>::run(o[2 * jp], pa, vb[0], vb[1]);
           Mma16816<T>::run(o[2 * jp + 1], pa, vb[2], vb[3]);
           if constexpr (kSplitP) {
@@ -284,7 +285,7 @@ paged_decode_combine_kernel(const DecodeParams p) {
     float acc = 0.f, L = 0.f;
     for (int s = 0; s < info.y; ++s) {
       const int64_t pi = static_cast<int64_t>(info.x + s) * p.num_heads + h;
-      const float wgt = exp2f(p.part_ml[pi * 2] - M);
+      const float wgt = fast_exp2(p.part_ml[pi * 2] - M);
       acc += wgt * p.part_o[pi * D + d];
       L += wgt * p.part_ml[pi * 2 + 1];
     }

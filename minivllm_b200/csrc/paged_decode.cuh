@@ -145,7 +145,7 @@ __device__ __forceinline__ void merge_and_write(const DecodeParams& p, const flo
     float acc = 0.f, L = 0.f;
 #pragma unroll
     for (int ww = 0; ww < kDecWarps; ++ww) {
-      const float wgt = exp2f(sML[(ww * 16 + row) * 2] - M);
+      const float wgt = fast_exp2(sML[(ww * 16 + row) * 2] - M);
       acc += wgt * sO[(ww * 16 + row) * stride + d];
       L += wgt * sML[(ww * 16 + row) * 2 + 1];
     }

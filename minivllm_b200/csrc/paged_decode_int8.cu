@@ -2,12 +2,16 @@
 // codes with fp16 scales, written by the quantising store_kvcache).
 //
 // Same plan, work items and warp-private cp.async rings as paged_decode.cu;
-// what differs is the operand path.  Codes are dequantised in registers:
-// a byte c becomes the fp16 value c exactly (byte-permute into 0x64xx =
-// 1024 + (c ^ 0x80), minus 1152), the MMAs run in fp16 with fp32 accumulation
-// whatever the model dtype (codes are integers <= 127, q is converted), and
-// the per-token scales are applied where they factor out: the K scale on the
-// score column, the V scale on the probability column.  The k index of the
+// what differs is the operand path.  Codes are dequantised in registers: a
+// byte c is byte-permuted into the fp16 pattern 0x64xx = 1024 + (c ^ 0x80) =
+// c + 1152 (exact), and the constant 1152 is NOT subtracted per element but
+// taken out afterwards where it factors: S = Q.(C + 1152) - 1152 * rowsum(Q),
+// O = P'.(C + 1152) - 1152 * rowsum(P'), the latter row sum coming from one
+// extra MMA against a tile of ones so that it is exactly what the tensor core
+// summed.  The MMAs run in fp16 with fp32 accumulation whatever the model
+// dtype (q is converted), and the per-token scales are applied where they
+// factor out: the K scale on the score column, the V scale on the
+// probability column.  The k index of the
 // QK^T MMAs and the n index of the PV MMAs are permuted so that every thread
 // reads its operands with 16-byte shared-memory loads.
 // HBM-bound: algorithmic bytes = sum(ctx) * num_kv_heads * (head_dim + 2) * 2.
@@ -15,13 +19,17 @@
 
 namespace mv {
 
-constexpr int kQStages = 6;  // an int8 tile is a quarter of an fp16 tile: deeper ring, same bytes in flight
+// A warp's loop iteration has a fixed latency (wait, dequantise, dependent MMAs, softmax shuffles) that is
+// about the same for 16 or 32 tokens, and int8 rows are half as long as fp16 rows: 32-token tiles keep the
+// bytes per iteration (8 KB) equal to the fp16 kernel's.
+constexpr int kQTok = 32;     // tokens per warp tile
+constexpr int kQStages = 3;
 constexpr int kQD = 128;
 
 struct Int8Smem {
   static constexpr int kRowBytes = kQD;                              // one row of codes
-  static constexpr int kTileBytes = kTileTok * kRowBytes;            // K or V codes of a tile
-  static constexpr int kScaleBytes = 2 * kTileTok * 4;               // one 4-byte word per token, K then V
+  static constexpr int kTileBytes = kQTok * kRowBytes;               // K or V codes of a tile
+  static constexpr int kScaleBytes = 2 * kQTok * 4;                  // one 4-byte word per token, K then V
   static constexpr int kStageBytes = 2 * kTileBytes + kScaleBytes;
   static constexpr int kWarpBytes = kQStages * kStageBytes;
   static constexpr int kRingBytes = kDecWarps * kWarpBytes;
@@ -48,12 +56,6 @@ __device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {
   asm("prmt.b32 %0, %1, %2, %3;" : "=r"(r) : "r"(a), "r"(b), "r"(sel));
   return r;
 }
-// Two biased bytes (c ^ 0x80) sitting in 0x64xx halves -> the two codes as fp16.
-__device__ __forceinline__ uint32_t unbias2(uint32_t h2) {
-  const __half2 k = __halves2half2(__ushort_as_half(0x6480), __ushort_as_half(0x6480));  // 1152
-  __half2 v = __hsub2(*reinterpret_cast<__half2*>(&h2), k);
-  return *reinterpret_cast<uint32_t*>(&v);
-}
 __device__ __forceinline__ float scale_of(uint32_t word, uint32_t odd) {
   return __half2float(__ushort_as_half(static_cast<unsigned short>(odd ? (word >> 16) : (word & 0xffffu))));
 }
@@ -69,7 +71,7 @@ paged_decode_int8_kernel(const DecodeParams p) {
 
   extern __shared__ __align__(128) unsigned char smem[];
   __shared__ long long s_red[kDecWarps];
-  __shared__ uint32_t s_mask[kDecWarps][kQStages];  // low 16 bits: live rows, high 16: scale index is odd
+  __shared__ uint32_t s_mask[kDecWarps][kQStages][2];  // [0]: live rows of the tile, [1]: rows whose scale index is odd
   int* s_start = reinterpret_cast<int*>(smem + S::kRingBytes);
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -100,40 +102,39 @@ paged_decode_int8_kernel(const DecodeParams p) {
     const int h0 = kvh * p.group + mt * 16;
 
     const int span = tok_end - tok_begin;
-    const int cta_tiles = span > 0 ? (span + kTileTok - 1) / kTileTok : 0;
+    const int cta_tiles = span > 0 ? (span + kQTok - 1) / kQTok : 0;
     const int my_tiles = cta_tiles > warp ? (cta_tiles - warp + kDecWarps - 1) / kDecWarps : 0;
 
     auto issue = [&](int i) {
       if (i < my_tiles) {
         const int stage = i % kQStages;
-        const int tok0 = tok_begin + (i * kDecWarps + warp) * kTileTok;
+        const int tok0 = tok_begin + (i * kDecWarps + warp) * kQTok;
         const int blk0 = tok0 / bs, off0 = tok0 - blk0 * bs;
-        const int r_me = lane & 15;  // lanes 16..31 mirror rows 0..15
-        int off = off0 + r_me, blk = blk0;
+        int off = off0 + lane, blk = blk0;           // lane r resolves row r of the tile
         while (off >= bs) { off -= bs; ++blk; }
         int slot = -1;
-        if (tok0 + r_me < tok_end) {
+        if (tok0 + lane < tok_end) {
           const int pb = __ldg(table + blk);
           if (pb >= 0 && pb < p.num_blocks) slot = pb * bs + off;
         }
         const int64_t sidx = static_cast<int64_t>(slot) * p.num_kv_heads + kvh;  // scale index of my row
-        const uint32_t live = __ballot_sync(0xffffffffu, slot >= 0) & 0xffffu;
-        const uint32_t odd = __ballot_sync(0xffffffffu, slot >= 0 && (sidx & 1)) & 0xffffu;
-        if (lane == 0) s_mask[warp][stage] = live | (odd << 16);
+        const bool is_odd = slot >= 0 && (sidx & 1);
+        const uint32_t live = __ballot_sync(0xffffffffu, slot >= 0);
+        const uint32_t odd = __ballot_sync(0xffffffffu, is_odd);
+        if (lane == 0) { s_mask[warp][stage][0] = live; s_mask[warp][stage][1] = odd; }
         const uint32_t kdst = ring + stage * S::kStageBytes;
         const uint32_t vdst = kdst + S::kTileBytes;
         const uint32_t sdst = vdst + S::kTileBytes;
-        // scales: lanes 0..15 fetch K, lanes 16..31 fetch V, one aligned 4-byte word holding the fp16
+        // scales: one aligned 4-byte word holding the fp16 (low or high half), K words then V words
         {
-          const __half* sp = lane < 16 ? p.k_scale : p.v_scale;
-          const bool is_odd = sidx & 1;
-          const void* src = slot >= 0 ? static_cast<const void*>(sp + (is_odd ? sidx - 1 : sidx))
-                                      : static_cast<const void*>(sp);
-          cp_async4(sdst + lane * 4, src, slot >= 0 ? (is_odd ? 4 : 2) : 0);
+          const int64_t base = slot >= 0 ? (is_odd ? sidx - 1 : sidx) : 0;
+          const int nbytes = slot >= 0 ? (is_odd ? 4 : 2) : 0;
+          cp_async4(sdst + lane * 4, p.k_scale + base, nbytes);
+          cp_async4(sdst + (kQTok + lane) * 4, p.v_scale + base, nbytes);
         }
         const int c = lane & 7, r0 = lane >> 3;
 #pragma unroll
-        for (int it = 0; it < 4; ++it) {
+        for (int it = 0; it < kQTok / 4; ++it) {
           const int r = r0 + it * 4;
           const int s = __shfl_sync(0xffffffffu, slot, r);
           const int64_t boff = s >= 0 ? (static_cast<int64_t>(s) * p.num_kv_heads + kvh) * D + c * 16 : 0;
@@ -173,10 +174,30 @@ paged_decode_int8_kernel(const DecodeParams p) {
       }
     }
 
+    // -1152 * sum over head_dim of q, per row: the bias of the un-subtracted codes in S
+    float nbias0 = 0.f, nbias1 = 0.f;
+#pragma unroll
+    for (int ks = 0; ks < KSTEPS; ++ks) {
+      const float2 a = __half22float2(*reinterpret_cast<const __half2*>(&qa[ks][0]));
+      const float2 b = __half22float2(*reinterpret_cast<const __half2*>(&qa[ks][2]));
+      const float2 c = __half22float2(*reinterpret_cast<const __half2*>(&qa[ks][1]));
+      const float2 d = __half22float2(*reinterpret_cast<const __half2*>(&qa[ks][3]));
+      nbias0 += (a.x + a.y) + (b.x + b.y);
+      nbias1 += (c.x + c.y) + (d.x + d.y);
+    }
+    nbias0 += __shfl_xor_sync(0xffffffffu, nbias0, 1);
+    nbias0 += __shfl_xor_sync(0xffffffffu, nbias0, 2);
+    nbias1 += __shfl_xor_sync(0xffffffffu, nbias1, 1);
+    nbias1 += __shfl_xor_sync(0xffffffffu, nbias1, 2);
+    nbias0 *= -1152.f;
+    nbias1 *= -1152.f;
+
     float o[NT][4];
 #pragma unroll
     for (int j = 0; j < NT; ++j) { o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.f; }
+    float osum[4] = {0.f, 0.f, 0.f, 0.f};   // P' times a tile of ones: row sums of P' as the tensor core adds them
     float m0 = kNegBig, m1 = kNegBig, l0 = 0.f, l1 = 0.f;
+    const uint32_t kOnes = 0x3c003c00u;     // fp16 (1, 1)
 
     for (int i = 0; i < my_tiles; ++i) {
       cp_async_wait<kQStages - 2>();
@@ -185,12 +206,12 @@ paged_decode_int8_kernel(const DecodeParams p) {
       const uint32_t kbase = ring + stage * S::kStageBytes;
       const uint32_t vbase = kbase + S::kTileBytes;
       const uint32_t sbase = vbase + S::kTileBytes;
-      const uint32_t mask = s_mask[warp][stage];
+      const uint32_t live = s_mask[warp][stage][0], odd = s_mask[warp][stage][1];
 
-      // ---- S = Q K^T on the codes ----
-      float s[2][4];
+      // ---- S = Q K^T on the codes: four n-tiles of 8 tokens ----
+      float s[4][4];
 #pragma unroll
-      for (int n = 0; n < 2; ++n) {
+      for (int n = 0; n < 4; ++n) {
         s[n][0] = s[n][1] = s[n][2] = s[n][3] = 0.f;
         const int row = 8 * n + g;
         const uint4 w0 = lds128(kbase + row * S::kRowBytes + (((2 * t) ^ (row & 7)) << 4));
@@ -199,9 +220,7 @@ paged_decode_int8_kernel(const DecodeParams p) {
 #pragma unroll
         for (int ks = 0; ks < KSTEPS; ++ks) {
           const uint32_t x = words[ks] ^ kBias;
-          const uint32_t b0 = unbias2(prmt(x, kMagic, 0x4140u));
-          const uint32_t b1 = unbias2(prmt(x, kMagic, 0x4342u));
-          Mma16816<__half>::run(s[n], qa[ks], b0, b1);
+          Mma16816<__half>::run(s[n], qa[ks], prmt(x, kMagic, 0x4140u), prmt(x, kMagic, 0x4342u));
         }
       }
       issue(i + kQStages - 1);
@@ -209,14 +228,14 @@ paged_decode_int8_kernel(const DecodeParams p) {
       // ---- K scales, mask, online softmax ----
       float mx0 = kNegBig, mx1 = kNegBig;
 #pragma unroll
-      for (int n = 0; n < 2; ++n) {
+      for (int n = 0; n < 4; ++n) {
 #pragma unroll
         for (int e2 = 0; e2 < 2; ++e2) {
           const int col = n * 8 + 2 * t + e2;
-          const bool ok = (mask >> col) & 1u;
-          const float ks = scale_of(lds32(sbase + col * 4), (mask >> (16 + col)) & 1u) * p.scale_log2;
-          s[n][e2] = ok ? s[n][e2] * ks : -INFINITY;
-          s[n][2 + e2] = ok ? s[n][2 + e2] * ks : -INFINITY;
+          const bool ok = (live >> col) & 1u;
+          const float ks = scale_of(lds32(sbase + col * 4), (odd >> col) & 1u) * p.scale_log2;
+          s[n][e2] = ok ? (s[n][e2] + nbias0) * ks : -INFINITY;
+          s[n][2 + e2] = ok ? (s[n][2 + e2] + nbias1) * ks : -INFINITY;
         }
         mx0 = fmaxf(mx0, fmaxf(s[n][0], s[n][1]));
         mx1 = fmaxf(mx1, fmaxf(s[n][2], s[n][3]));
@@ -226,30 +245,37 @@ paged_decode_int8_kernel(const DecodeParams p) {
       mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
       mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
       const float mn0 = fmaxf(m0, mx0), mn1 = fmaxf(m1, mx1);
-      const float a0 = exp2f(m0 - mn0), a1 = exp2f(m1 - mn1);
+      const float a0 = fast_exp2(m0 - mn0), a1 = fast_exp2(m1 - mn1);
       m0 = mn0; m1 = mn1;
       float ps0 = 0.f, ps1 = 0.f;
-      uint32_t pa[4];
+      uint32_t pa[2][4];   // A fragments of the two 16-token k-steps
 #pragma unroll
-      for (int n = 0; n < 2; ++n) {
-        const float p00 = exp2f(s[n][0] - mn0), p01 = exp2f(s[n][1] - mn0);
-        const float p10 = exp2f(s[n][2] - mn1), p11 = exp2f(s[n][3] - mn1);
+      for (int n = 0; n < 4; ++n) {
+        const float p00 = fast_exp2(s[n][0] - mn0), p01 = fast_exp2(s[n][1] - mn0);
+        const float p10 = fast_exp2(s[n][2] - mn1), p11 = fast_exp2(s[n][3] - mn1);
         ps0 += p00 + p01;
         ps1 += p10 + p11;
         // V scale of the two tokens of this column pair, folded into P
         const int col = n * 8 + 2 * t;
-        const float vs0 = scale_of(lds32(sbase + (16 + col) * 4), (mask >> (16 + col)) & 1u);
-        const float vs1 = scale_of(lds32(sbase + (17 + col) * 4), (mask >> (17 + col)) & 1u);
-        const bool ok0 = (mask >> col) & 1u, ok1 = (mask >> (col + 1)) & 1u;
-        pa[2 * n] = pack2<__half>(ok0 ? p00 * vs0 : 0.f, ok1 ? p01 * vs1 : 0.f);
-        pa[2 * n + 1] = pack2<__half>(ok0 ? p10 * vs0 : 0.f, ok1 ? p11 * vs1 : 0.f);
+        const float vs0 = scale_of(lds32(sbase + (kQTok + col) * 4), (odd >> col) & 1u);
+        const float vs1 = scale_of(lds32(sbase + (kQTok + col + 1) * 4), (odd >> (col + 1)) & 1u);
+        const bool ok0 = (live >> col) & 1u, ok1 = (live >> (col + 1)) & 1u;
+        pa[n >> 1][2 * (n & 1)] = pack2<__half>(ok0 ? p00 * vs0 : 0.f, ok1 ? p01 * vs1 : 0.f);
+        pa[n >> 1][2 * (n & 1) + 1] = pack2<__half>(ok0 ? p10 * vs0 : 0.f, ok1 ? p11 * vs1 : 0.f);
       }
       l0 = l0 * a0 + ps0;
       l1 = l1 * a1 + ps1;
 
+      // the running maximum rarely moves after the first tiles: rescale only when some row of the warp needs it
+      if (__any_sync(0xffffffffu, a0 != 1.f || a1 != 1.f)) {
+#pragma unroll
+        for (int j = 0; j < NT; ++j) { o[j][0] *= a0; o[j][1] *= a0; o[j][2] *= a1; o[j][3] *= a1; }
+        osum[0] *= a0; osum[1] *= a0; osum[2] *= a1; osum[3] *= a1;
+      }
       // ---- O += P V on the codes; n-tile j of thread (g, t) is head-dim element 16*col + j ----
-      {
-        const int ra = 2 * t, rb = 2 * t + 1, rc = 2 * t + 8, rd = 2 * t + 9;
+#pragma unroll
+      for (int kk = 0; kk < 2; ++kk) {
+        const int ra = 16 * kk + 2 * t, rb = ra + 1, rc = ra + 8, rd = ra + 9;
         const uint4 va = lds128(vbase + ra * S::kRowBytes + ((g ^ (ra & 7)) << 4));
         const uint4 vb = lds128(vbase + rb * S::kRowBytes + ((g ^ (rb & 7)) << 4));
         const uint4 vcx = lds128(vbase + rc * S::kRowBytes + ((g ^ (rc & 7)) << 4));
@@ -259,19 +285,16 @@ paged_decode_int8_kernel(const DecodeParams p) {
 #pragma unroll
         for (int wi = 0; wi < 4; ++wi) {
           const uint32_t xa = wa[wi] ^ kBias, xb = wb[wi] ^ kBias, xc = wc[wi] ^ kBias, xd = wd[wi] ^ kBias;
-          const uint32_t lo01 = prmt(xa, xb, 0x5140u), lo23 = prmt(xa, xb, 0x7362u);  // tokens 2t, 2t+1
-          const uint32_t hi01 = prmt(xc, xd, 0x5140u), hi23 = prmt(xc, xd, 0x7362u);  // tokens 2t+8, 2t+9
+          const uint32_t lo01 = prmt(xa, xb, 0x5140u), lo23 = prmt(xa, xb, 0x7362u);  // tokens ra, ra+1
+          const uint32_t hi01 = prmt(xc, xd, 0x5140u), hi23 = prmt(xc, xd, 0x7362u);  // tokens ra+8, ra+9
           const uint32_t lo[4] = {prmt(lo01, kMagic, 0x4140u), prmt(lo01, kMagic, 0x4342u),
                                   prmt(lo23, kMagic, 0x4140u), prmt(lo23, kMagic, 0x4342u)};
           const uint32_t hi[4] = {prmt(hi01, kMagic, 0x4140u), prmt(hi01, kMagic, 0x4342u),
                                   prmt(hi23, kMagic, 0x4140u), prmt(hi23, kMagic, 0x4342u)};
 #pragma unroll
-          for (int jj = 0; jj < 4; ++jj) {
-            float* oj = o[4 * wi + jj];
-            oj[0] *= a0; oj[1] *= a0; oj[2] *= a1; oj[3] *= a1;
-            Mma16816<__half>::run(o[4 * wi + jj], pa, unbias2(lo[jj]), unbias2(hi[jj]));
-          }
+          for (int jj = 0; jj < 4; ++jj) Mma16816<__half>::run(o[4 * wi + jj], pa[kk], lo[jj], hi[jj]);
         }
+        Mma16816<__half>::run(osum, pa[kk], kOnes, kOnes);
       }
       __syncwarp();
     }
@@ -281,6 +304,13 @@ paged_decode_int8_kernel(const DecodeParams p) {
     l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
     l1 += __shfl_xor_sync(0xffffffffu, l1, 1);
     l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
+
+    // every column of the ones tile carries the same row sum: take the bias of the V codes out of O
+    {
+      const float b0 = 1152.f * osum[0], b1 = 1152.f * osum[2];
+#pragma unroll
+      for (int j = 0; j < NT; ++j) { o[j][0] -= b0; o[j][1] -= b0; o[j][2] -= b1; o[j][3] -= b1; }
+    }
 
     __syncthreads();
     float* sO = reinterpret_cast<float*>(smem);

@@ -95,18 +95,21 @@ __device__ __forceinline__ void quant_chunk(const uint4& raw, bool live, uint2& 
   for (int j = 0; j < 8; ++j) amax = fmaxf(amax, fabsf(x[j]));
 #pragma unroll
   for (int off = GROUP / 2; off > 0; off >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, off));
-  float s = 0.f, inv = 0.f;
-  if ((threadIdx.x & (GROUP - 1)) == 0) {
-    s = __half2float(__float2half_rn(__fdiv_rn(amax, 127.f)));
-    inv = (s >= 6.103515625e-05f && s < INFINITY) ? __frcp_rn(s) : 0.f;  // 0 marks "take the exact path"
-  }
-  const int leader = (threadIdx.x & 31) & ~(GROUP - 1);
-  s = __shfl_sync(0xffffffffu, s, leader);
-  inv = __shfl_sync(0xffffffffu, inv, leader);
-  scale16 = __float2half_rn(s);  // s is an fp16 value already: exact
+  // amax is the same in every lane of the group, so every lane computes the scale itself (no leader branch):
+  // fp32(amax / 127) correctly rounded by the multiply-and-correct sequence for division by a constant
+  // (q0 = amax * RN(1/127); r = amax - 127*q0 exactly by FMA; q = q0 + r * RN(1/127)), then fp16.
+  constexpr float kInv127 = 0x1.020408p-7f;
+  const float q0 = amax * kInv127;
+  const float quo = fmaf(fmaf(-q0, 127.f, amax), kInv127, q0);
+  scale16 = __float2half_rn(quo);
+  const float s = __half2float(scale16);
+  // An approximate reciprocal is enough for the fast path (its error is covered by the near-tie gate below);
+  // 0 marks "take the exact path": scale zero, infinite or not a normal fp16 number.
+  float inv = 0.f;
+  if (s >= 6.103515625e-05f && s < INFINITY) asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(inv) : "f"(s));
 
   constexpr float kMagic = 12582912.f;  // 1.5 * 2^23: adding it rounds to nearest-even integer
-  constexpr float kNearTie = 0.4999f;   // product error is < 127 * 2^-23 = 1.6e-5: anything closer to k + 1/2 is re-done
+  constexpr float kNearTie = 0.4999f;   // product error is < 127 * 2^-21 = 6e-5 (approximate reciprocal + rounding): anything closer to k + 1/2 is re-done
   uint32_t t[8];
   float dist[8], worst = 0.f;
 #pragma unroll
