@@ -154,6 +154,29 @@ int mv_prefill_varlen(void* out, const void* q, const void* k, const void* v,
                       int* error_word, int dtype, void* stream);
 
 /*
+ * Prefill attention with a cached prefix (or a chunk of a longer prompt):
+ * the queries are the packed UNCACHED tokens (cu_seqlens_q), the keys and
+ * values are read from the paged cache through block_tables, which must
+ * already hold every token of the step (store_kvcache first).  Sequence s has
+ * k_s = cu_seqlens_k[s+1]-cu_seqlens_k[s] keys and q_s queries; query i sits
+ * at position k_s - q_s + i and attends to keys at positions <= its own.
+ * This is the case the reference prepares (src/myvllm/engine/model_runner.py
+ * :198-215 builds cu_seqlens_k != cu_seqlens_q and block_tables on a prefix
+ * hit) but never computes: its prefill kernel indexes K/V with the query
+ * offsets (src/myvllm/layers/attention.py:135-137,171,194).  block_size must
+ * divide 128 (multiple of 8) or be a multiple of 128.  Same error_word
+ * contract as mv_prefill_varlen.
+ */
+int mv_prefill_paged(void* out, const void* q, int64_t q_stride_tok,
+                     const void* k_cache, const void* v_cache,
+                     const int32_t* cu_seqlens_q, const int32_t* cu_seqlens_k,
+                     const int32_t* block_tables, int64_t bt_stride,
+                     int max_blocks, int block_size, int64_t num_blocks,
+                     int num_seqs, int64_t total_q_tokens, int num_heads,
+                     int num_kv_heads, int head_dim, float scale,
+                     int* error_word, int dtype, void* stream);
+
+/*
  * Per-step metadata, built on the GPU from persistent per-sequence state.
  * State (device memory, owned by the caller, one row per sequence "slot"):
  *   tables (num_slots, max_blocks) int32 block table rows, -1 = none;

@@ -36,6 +36,8 @@ SIGNATURES = {
                                         _c_int, _c_ptr]),
     "mv_prefill_varlen": (_c_int, [_c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_i64, _c_i64, _c_i64, _c_ptr, _c_int, _c_i64,
                                    _c_int, _c_int, _c_int, _c_f32, _c_ptr, _c_int, _c_ptr]),
+    "mv_prefill_paged": (_c_int, [_c_ptr, _c_ptr, _c_i64, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_i64, _c_int, _c_int,
+                                  _c_i64, _c_int, _c_i64, _c_int, _c_int, _c_int, _c_f32, _c_ptr, _c_int, _c_ptr]),
     "mv_build_decode_meta": (_c_int, [_c_ptr, _c_ptr, _c_int, _c_ptr, _c_i64, _c_int, _c_int, _c_ptr, _c_ptr,
                                       _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_i64, _c_ptr]),
     "mv_build_prefill_meta": (_c_int, [_c_ptr, _c_ptr, _c_ptr, _c_int, _c_i64, _c_ptr, _c_i64, _c_int, _c_int,

@@ -19,8 +19,10 @@
 // is a TS MMA (P from tensor memory, V from shared memory, MN-major).  The
 // running maximum is only moved when it grows by more than 2^8, so O in tensor
 // memory is rescaled rarely; l and the final 1/l use the same stale maximum.
-// KV tiles above the diagonal are never visited; only the diagonal tile is
-// masked.  No cluster multicast anywhere.
+// KV tiles above the diagonal are never visited; only tiles that reach past
+// the first row's position are masked.  In paged mode (a cached prefix, or a
+// chunk of a longer prompt) K and V come from the paged cache through the
+// block tables instead of the packed inputs.  No cluster multicast anywhere.
 //
 // Tensor-bound: FLOPs = 4 * heads * head_dim * sum_s L_s (L_s + 1) / 2.
 #include <cuda.h>
@@ -51,6 +53,13 @@ struct PrefillParams {
   float scale_log2;
   int fmt;          // 0 fp16, 1 bf16
   int* error_word;
+  // Paged mode (prefix hit / chunked prefill): K and V are read from the paged cache through the block
+  // tables, and sequence s has cu_seqlens_k-many keys of which the first (keys - queries) are already cached.
+  int paged;
+  const int32_t* cu_seqlens_k;
+  const int32_t* block_tables;
+  int64_t bt_stride;
+  int max_blocks, block_size, box_rows;   // box_rows = min(block_size, 128): rows of one TMA box of the cache
 };
 
 enum { BAR_Q = 0, BAR_KFULL = 1, BAR_KEMPTY = 3, BAR_VFULL = 5, BAR_VEMPTY = 7, BAR_SFULL = 9, BAR_PREADY = 11,
@@ -148,12 +157,17 @@ prefill_varlen_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
   const int seq_start = p.cu_seqlens[seq];
   const int seq_len = p.cu_seqlens[seq + 1] - seq_start;
   const int q0 = qtile * kPfTile;              // first query row of the tile within the sequence
-  const int n_kv = qtile + 1;                  // causal: KV tiles 0..qtile
-  // Rows of the first query tile have fewer than 128 keys, so the rounding of
-  // their weights to bf16 (8 significant bits) does not average out: those
-  // CTAs (the cheapest ones) also feed the rounding residue of P through a
-  // second PV MMA.  fp16 P has 11 bits and needs nothing.
-  const bool split_p = std::is_same<T, __nv_bfloat16>::value && n_kv == 1;
+  // keys of this sequence that precede its first query row (0 unless paged: a cached prefix)
+  const int n_cached = p.paged ? (p.cu_seqlens_k[seq + 1] - p.cu_seqlens_k[seq]) - seq_len : 0;
+  const int first_pos = n_cached + q0;         // position of the tile's first query row within the sequence
+  // causal: KV tiles up to the one holding the position of the tile's last real query row
+  const int n_kv = (n_cached + min(q0 + kPfTile, seq_len) + kPfTile - 1) / kPfTile;
+  // A tile whose first row sits below position 128 has rows with fewer than 128
+  // keys, so the rounding of their weights to bf16 (8 significant bits) does not
+  // average out: those CTAs (the cheapest ones, one or two KV tiles) also feed
+  // the rounding residue of P through a second PV MMA.  fp16 P has 11 bits and
+  // needs nothing.
+  const bool split_p = std::is_same<T, __nv_bfloat16>::value && first_pos < kPfTile;
 
   if (tid == 0) {
     tc::mbar_init(bar(BAR_Q), 1);
@@ -192,18 +206,34 @@ prefill_varlen_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
         for (int t = 0; t < (has_b ? 2 : 1); ++t)
           for (int h = 0; h < 2; ++h)
             tc::tma_load_3d(q_smem + t * kPfTileBytes + h * kPfHalfBytes, &tmap_q, 64 * h, head_a + t, row0, bar(BAR_Q));
+        // One 128-token K or V tile: packed rows of this sequence, or (paged) the cache rows that the block
+        // table gives for positions 128j.., as 128 / box_rows boxes of box_rows rows each.  A table entry
+        // that is missing loads block 0: those keys lie beyond every query row of the tile and are masked.
+        auto load_kv_tile = [&](const CUtensorMap* tm, uint32_t dst, int j, uint32_t full_bar) {
+          if (!p.paged) {
+            for (int h = 0; h < 2; ++h)
+              tc::tma_load_3d(dst + h * kPfHalfBytes, tm, 64 * h, kvh, seq_start + j * kPfTile, full_bar);
+            return;
+          }
+          const int32_t* table = p.block_tables + static_cast<int64_t>(seq) * p.bt_stride;
+          for (int r = 0; r < kPfTile / p.box_rows; ++r) {
+            const int pos = j * kPfTile + r * p.box_rows;
+            const int blk = pos / p.block_size, off = pos - blk * p.block_size;
+            const int phys = blk < p.max_blocks ? table[blk] : -1;
+            const int slot = phys >= 0 ? phys * p.block_size + off : 0;
+            for (int h = 0; h < 2; ++h)
+              tc::tma_load_3d(dst + h * kPfHalfBytes + r * p.box_rows * 128, tm, 64 * h, kvh, slot, full_bar);
+          }
+        };
         for (int j = 0; j < n_kv; ++j) {
           const int s = j % kPfStages;
           const uint32_t ph = ((j / kPfStages) & 1) ^ 1;
-          const int krow = seq_start + j * kPfTile;
           tc::mbar_wait(bar(BAR_KEMPTY + s), ph, abort_flag, p.error_word, 1);
           tc::mbar_expect_tx(bar(BAR_KFULL + s), kPfTileBytes);
-          for (int h = 0; h < 2; ++h)
-            tc::tma_load_3d(k_smem + s * kPfTileBytes + h * kPfHalfBytes, &tmap_k, 64 * h, kvh, krow, bar(BAR_KFULL + s));
+          load_kv_tile(&tmap_k, k_smem + s * kPfTileBytes, j, bar(BAR_KFULL + s));
           tc::mbar_wait(bar(BAR_VEMPTY + s), ph, abort_flag, p.error_word, 2);
           tc::mbar_expect_tx(bar(BAR_VFULL + s), kPfTileBytes);
-          for (int h = 0; h < 2; ++h)
-            tc::tma_load_3d(v_smem + s * kPfTileBytes + h * kPfHalfBytes, &tmap_v, 64 * h, kvh, krow, bar(BAR_VFULL + s));
+          load_kv_tile(&tmap_v, v_smem + s * kPfTileBytes, j, bar(BAR_VFULL + s));
         }
       }
     } else if (warp == 9) {
@@ -320,7 +350,11 @@ prefill_varlen_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
         tc::fence_after_sync();
         if (tid == 0) PF_STAMP(0, j, 0);
         if (tid == 128) PF_STAMP(1, j, 0);
-        const bool diag = j == n_kv - 1;
+        // Keys of this tile sit at positions 128j + col, query row r at first_pos + r: a key is visible when
+        // col <= r + shift.  Tiles that end at or before the first row's position need no mask at all.
+        const int shift = first_pos - j * kPfTile;
+        const bool diag = shift < kPfTile - 1;
+        const int vis = row + shift;            // last visible column of this thread's row
         float sum = 0.f;
         if (!split_p) {
           // ---- fast path: the whole S row in registers, one wait for four loads ----
@@ -334,7 +368,7 @@ prefill_varlen_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
             for (int c = 0; c < 4; ++c)
 #pragma unroll
               for (int i = 0; i < 32; ++i)
-                if (c * 32 + i > row) sv[c][i] = 0xff800000u;  // -inf
+                if (c * 32 + i > vis) sv[c][i] = 0xff800000u;  // -inf
           }
           // Row maximum: three-input max, eight independent chains (one chain of 128 dependent ops costs ~500 cycles).
           float mxs[8];
@@ -378,7 +412,7 @@ prefill_varlen_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
           const float2 s01 = tc::add2(sums[0], sums[1]), s23 = tc::add2(sums[2], sums[3]);
           sum = (s01.x + s01.y) + (s23.x + s23.y);
         } else {
-          // ---- first query tile in bf16: two passes over S, P plus its rounding residue ----
+          // ---- rows with few keys, bf16: two passes over S, P plus its rounding residue ----
           float mx = -INFINITY;
 #pragma unroll
           for (int c = 0; c < 4; ++c) {
@@ -387,9 +421,12 @@ prefill_varlen_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
             tc::wait_ld();
 #pragma unroll
             for (int i = 0; i < 32; ++i)
-              mx = fmaxf(mx, (diag && c * 32 + i > row) ? -INFINITY : __uint_as_float(sv[i]));
+              mx = fmaxf(mx, (diag && c * 32 + i > vis) ? -INFINITY : __uint_as_float(sv[i]));
           }
-          m_used = mx * p.scale_log2;   // split_p implies a single KV tile: j == 0, nothing to rescale
+          mx *= p.scale_log2;
+          const bool grow = mx > m_used + kRescaleThreshold;
+          if (j > 0 && __any_sync(0xffffffffu, grow)) rescale_o(grow ? ex2(m_used - mx) : 1.f, j, l);
+          if (grow) m_used = mx;
           uint32_t plo[32];
 #pragma unroll
           for (int c2 = 0; c2 < 2; ++c2) {
@@ -404,8 +441,8 @@ prefill_varlen_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
               const int k = (i & 15) * 2, col = c2 * 64 + 2 * i;
               float s0 = __uint_as_float(i < 16 ? sa[k] : sb[k]);
               float s1 = __uint_as_float(i < 16 ? sa[k + 1] : sb[k + 1]);
-              if (diag && col > row) s0 = -INFINITY;
-              if (diag && col + 1 > row) s1 = -INFINITY;
+              if (diag && col > vis) s0 = -INFINITY;
+              if (diag && col + 1 > vis) s1 = -INFINITY;
               const float p0 = ex2(fmaf(s0, p.scale_log2, -m_used));
               const float p1 = ex2(fmaf(s1, p.scale_log2, -m_used));
               pk[i] = pack2<T>(p0, p1);
@@ -479,13 +516,14 @@ static EncodeTiledFn encode_tiled_fn() {
 }
 
 // (tokens, heads, 128) tensor, token stride given; box = 64 elements x 1 head x 128 tokens, 128B swizzle.
-static int make_tmap(CUtensorMap* m, const void* base, int64_t tokens, int heads, int64_t stride_tok, int dtype) {
+static int make_tmap(CUtensorMap* m, const void* base, int64_t tokens, int heads, int64_t stride_tok, int dtype,
+                     int box_rows = kPfTile) {
   EncodeTiledFn fn = encode_tiled_fn();
   if (!fn) return fail(MV_ERR_CUDA, "prefill: cuTensorMapEncodeTiled is not available");
   const cuuint64_t dims[3] = {static_cast<cuuint64_t>(kPfD), static_cast<cuuint64_t>(heads),
                               static_cast<cuuint64_t>(tokens)};
   const cuuint64_t strides[2] = {static_cast<cuuint64_t>(kPfD) * 2, static_cast<cuuint64_t>(stride_tok) * 2};
-  const cuuint32_t box[3] = {64, 1, static_cast<cuuint32_t>(kPfTile)};
+  const cuuint32_t box[3] = {64, 1, static_cast<cuuint32_t>(box_rows)};
   const cuuint32_t estr[3] = {1, 1, 1};
   const CUresult r = fn(m, dtype == MV_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3,
                         const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
@@ -504,6 +542,37 @@ extern "C" int mv_debug_prefill_trace(long long* buffer, int cta) {
   return 0;
 }
 #endif
+
+namespace mv {
+static int launch_prefill(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, PrefillParams& p,
+                          int64_t total_tokens, int num_seqs, int num_kv_heads, int dtype, void* stream) {
+  // Upper bound on the number of query tiles, from shapes only: no host sync.
+  const int64_t max_tiles = (total_tokens + kPfTile - 1) / kPfTile + num_seqs;
+  if (max_tiles > 0x7fffffffLL || static_cast<int64_t>(num_kv_heads) * p.pairs > 65535)
+    return fail(MV_ERR_LIMIT, "prefill: grid too large");
+  const dim3 grid(static_cast<unsigned>(max_tiles), static_cast<unsigned>(num_kv_heads * p.pairs));
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  static bool attr_done[64][2] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  const int ti = dtype == MV_F16 ? 0 : 1;
+  if (dev < 0 || dev >= 64 || !attr_done[dev][ti]) {
+    const cudaError_t e =
+        ti == 0 ? cudaFuncSetAttribute(prefill_varlen_kernel<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       kPfSmemBytes)
+                : cudaFuncSetAttribute(prefill_varlen_kernel<__nv_bfloat16>,
+                                       cudaFuncAttributeMaxDynamicSharedMemorySize, kPfSmemBytes);
+    if (e != cudaSuccess) {
+      cudaGetLastError();
+      return fail(MV_ERR_CUDA, "prefill: cudaFuncSetAttribute: %s", cudaGetErrorString(e));
+    }
+    if (dev >= 0 && dev < 64) attr_done[dev][ti] = true;
+  }
+  if (ti == 0) prefill_varlen_kernel<__half><<<grid, kPfThreads, kPfSmemBytes, st>>>(tq, tk, tv, p);
+  else prefill_varlen_kernel<__nv_bfloat16><<<grid, kPfThreads, kPfSmemBytes, st>>>(tq, tk, tv, p);
+  return check_launch("prefill_varlen_kernel");
+}
+}  // namespace mv
 
 extern "C" int mv_prefill_varlen(void* out, const void* q, const void* k, const void* v, int64_t q_stride_tok,
                                  int64_t k_stride_tok, int64_t v_stride_tok, const int32_t* cu_seqlens, int num_seqs,
@@ -545,29 +614,68 @@ extern "C" int mv_prefill_varlen(void* out, const void* q, const void* k, const 
   p.scale_log2 = scale * 1.4426950408889634f;
   p.fmt = dtype == MV_F16 ? 0 : 1;
   p.error_word = error_word;
-  // Upper bound on the number of query tiles, from shapes only: no host sync.
-  const int64_t max_tiles = (total_tokens + kPfTile - 1) / kPfTile + num_seqs;
-  if (max_tiles > 0x7fffffffLL || static_cast<int64_t>(num_kv_heads) * p.pairs > 65535)
-    return fail(MV_ERR_LIMIT, "prefill: grid too large");
-  const dim3 grid(static_cast<unsigned>(max_tiles), static_cast<unsigned>(num_kv_heads * p.pairs));
-  cudaStream_t st = static_cast<cudaStream_t>(stream);
-  static bool attr_done[64][2] = {};
-  int dev = 0;
-  cudaGetDevice(&dev);
-  const int ti = dtype == MV_F16 ? 0 : 1;
-  if (dev < 0 || dev >= 64 || !attr_done[dev][ti]) {
-    const cudaError_t e =
-        ti == 0 ? cudaFuncSetAttribute(prefill_varlen_kernel<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                       kPfSmemBytes)
-                : cudaFuncSetAttribute(prefill_varlen_kernel<__nv_bfloat16>,
-                                       cudaFuncAttributeMaxDynamicSharedMemorySize, kPfSmemBytes);
-    if (e != cudaSuccess) {
-      cudaGetLastError();
-      return fail(MV_ERR_CUDA, "prefill: cudaFuncSetAttribute: %s", cudaGetErrorString(e));
-    }
-    if (dev >= 0 && dev < 64) attr_done[dev][ti] = true;
-  }
-  if (ti == 0) prefill_varlen_kernel<__half><<<grid, kPfThreads, kPfSmemBytes, st>>>(tq, tk, tv, p);
-  else prefill_varlen_kernel<__nv_bfloat16><<<grid, kPfThreads, kPfSmemBytes, st>>>(tq, tk, tv, p);
-  return check_launch("prefill_varlen_kernel");
+  p.paged = 0;
+  p.cu_seqlens_k = nullptr;
+  p.block_tables = nullptr;
+  p.bt_stride = 0;
+  p.max_blocks = 0;
+  p.block_size = kPfTile;
+  p.box_rows = kPfTile;
+  return launch_prefill(tq, tk, tv, p, total_tokens, num_seqs, num_kv_heads, dtype, stream);
+}
+
+extern "C" int mv_prefill_paged(void* out, const void* q, int64_t q_stride_tok, const void* k_cache,
+                                const void* v_cache, const int32_t* cu_seqlens_q, const int32_t* cu_seqlens_k,
+                                const int32_t* block_tables, int64_t bt_stride, int max_blocks, int block_size,
+                                int64_t num_blocks, int num_seqs, int64_t total_q_tokens, int num_heads,
+                                int num_kv_heads, int head_dim, float scale, int* error_word, int dtype,
+                                void* stream) {
+  using namespace mv;
+  if (dtype != MV_F16 && dtype != MV_BF16) return fail(MV_ERR_DTYPE, "prefill_paged: dtype %d", dtype);
+  if (num_seqs < 0 || total_q_tokens < 0 || num_heads <= 0 || num_kv_heads <= 0 || max_blocks <= 0 || num_blocks <= 0)
+    return fail(MV_ERR_SHAPE, "prefill_paged: negative or zero size");
+  if (num_heads % num_kv_heads != 0)
+    return fail(MV_ERR_SHAPE, "prefill_paged: num_heads %d is not a multiple of num_kv_heads %d", num_heads, num_kv_heads);
+  if (head_dim != kPfD) return fail(MV_ERR_SHAPE, "prefill_paged: head_dim %d is not 128", head_dim);
+  // one KV tile is 128 cache rows: whole blocks (block_size divides 128, multiple of 8) or part of one block
+  if (block_size < 8 || block_size % 8 != 0 || (block_size % kPfTile != 0 && kPfTile % block_size != 0))
+    return fail(MV_ERR_SHAPE, "prefill_paged: block_size %d must divide 128 (and be a multiple of 8) or be a multiple of 128",
+                block_size);
+  if (num_seqs == 0 || total_q_tokens == 0) return MV_OK;
+  if (!out || !q || !k_cache || !v_cache || !cu_seqlens_q || !cu_seqlens_k || !block_tables || !error_word)
+    return fail(MV_ERR_NULL, "prefill_paged: null pointer");
+  if (!aligned16(out) || !aligned16(q) || !aligned16(k_cache) || !aligned16(v_cache) || q_stride_tok % 8)
+    return fail(MV_ERR_ALIGN, "prefill_paged: pointers and token strides must be 16-byte aligned");
+  if (q_stride_tok < static_cast<int64_t>(num_heads) * head_dim)
+    return fail(MV_ERR_SHAPE, "prefill_paged: token stride smaller than a row");
+  if (bt_stride < max_blocks) return fail(MV_ERR_SHAPE, "prefill_paged: block table stride smaller than its width");
+  const int64_t num_slots = num_blocks * block_size;
+  if (total_q_tokens > 0x7fffffffLL || num_slots > 0x7fffffffLL) return fail(MV_ERR_LIMIT, "prefill_paged: more than 2^31 rows");
+  const int box_rows = block_size < kPfTile ? block_size : kPfTile;
+  CUtensorMap tq, tk, tv;
+  int rc = make_tmap(&tq, q, total_q_tokens, num_heads, q_stride_tok, dtype);
+  if (rc) return rc;
+  const int64_t cache_row = static_cast<int64_t>(num_kv_heads) * head_dim;
+  if ((rc = make_tmap(&tk, k_cache, num_slots, num_kv_heads, cache_row, dtype, box_rows))) return rc;
+  if ((rc = make_tmap(&tv, v_cache, num_slots, num_kv_heads, cache_row, dtype, box_rows))) return rc;
+  PrefillParams p;
+  p.out = out;
+  p.out_stride_tok = static_cast<int64_t>(num_heads) * head_dim;
+  p.cu_seqlens = cu_seqlens_q;
+  p.num_seqs = num_seqs;
+  p.num_heads = num_heads;
+  p.num_kv_heads = num_kv_heads;
+  p.group = num_heads / num_kv_heads;
+  p.pairs = (p.group + 1) / 2;
+  p.scale_log2 = scale * 1.4426950408889634f;
+  p.fmt = dtype == MV_F16 ? 0 : 1;
+  p.error_word = error_word;
+  p.paged = 1;
+  p.cu_seqlens_k = cu_seqlens_k;
+  p.block_tables = block_tables;
+  p.bt_stride = bt_stride;
+  p.max_blocks = max_blocks;
+  p.block_size = block_size;
+  p.box_rows = box_rows;
+  return launch_prefill(tq, tk, tv, p, total_q_tokens, num_seqs, num_kv_heads, dtype, stream);
 }

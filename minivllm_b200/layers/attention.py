@@ -200,6 +200,44 @@ def flash_attention_prefill(q, k, v, cu_seqlens, scale, num_heads, num_kv_heads,
     return out
 
 
+def flash_attention_prefill_paged(q, k_cache, v_cache, cu_seqlens_q, cu_seqlens_k, block_tables, scale, num_heads,
+                                  num_kv_heads, head_dim):
+    """Prefill attention when part of every sequence is already in the paged cache (prefix hit, or a later
+    chunk of a long prompt): q holds the packed uncached tokens, K and V are read from the cache through
+    `block_tables`, which must already contain this step's tokens (store first).  Query i of sequence s sits at
+    position (keys_s - queries_s + i) and attends to keys at positions <= its own.
+
+    The reference builds exactly this metadata on a prefix hit (src/myvllm/engine/model_runner.py:198-215) but
+    its kernel ignores it and attends to the uncached suffix only (src/myvllm/layers/attention.py:135-137).
+    """
+    _cabi.require_cuda(q, k_cache, v_cache, cu_seqlens_q, cu_seqlens_k, block_tables)
+    total = q.shape[0]
+    if tuple(q.shape) != (total, num_heads, head_dim):
+        raise ValueError(f"q shape {tuple(q.shape)} is not (tokens, {num_heads}, {head_dim})")
+    if k_cache.dim() != 4 or k_cache.shape != v_cache.shape or tuple(k_cache.shape[2:]) != (num_kv_heads, head_dim) \
+            or k_cache.dtype != q.dtype or v_cache.dtype != q.dtype or not k_cache.is_contiguous() \
+            or not v_cache.is_contiguous():
+        raise ValueError("caches must be contiguous (blocks, block_size, kv_heads, head_dim) tensors of q's dtype")
+    for t in (cu_seqlens_q, cu_seqlens_k):
+        if t.dtype != torch.int32 or t.dim() != 1 or not t.is_contiguous() or t.numel() != cu_seqlens_q.numel():
+            raise ValueError("cu_seqlens_q / cu_seqlens_k must be contiguous int32 vectors of equal length")
+    num_seqs = cu_seqlens_q.numel() - 1
+    if block_tables.dtype != torch.int32 or block_tables.dim() != 2 or block_tables.shape[0] != num_seqs or \
+            block_tables.stride(1) != 1:
+        raise ValueError("block_tables must be a (num_seqs, max_blocks) int32 tensor with dense rows")
+    out = torch.empty((total, num_heads, head_dim), dtype=q.dtype, device=q.device)
+    if total == 0 or num_seqs <= 0:
+        return out
+    rc = _cabi.lib().mv_prefill_paged(
+        out.data_ptr(), q.data_ptr(), _row_stride(q, "q"), k_cache.data_ptr(), v_cache.data_ptr(),
+        cu_seqlens_q.data_ptr(), cu_seqlens_k.data_ptr(), block_tables.data_ptr(),
+        block_tables.stride(0) if num_seqs > 1 else block_tables.shape[1], block_tables.shape[1], k_cache.shape[1],
+        k_cache.shape[0], num_seqs, total, num_heads, num_kv_heads, head_dim, float(scale),
+        _error_word(q.device).data_ptr(), _cabi.dtype_code(q.dtype), _cabi.stream_ptr())
+    _cabi.check(rc)
+    return out
+
+
 def qk_norm_rope_store(qkv, positions, cos_table, sin_table, gamma_q, gamma_k, eps, num_heads, num_kv_heads,
                        head_dim, k_cache=None, v_cache=None, slot_mapping=None):
     """One launch for what the reference does in a dozen before attention: RMSNorm of the q and k heads,
@@ -279,8 +317,14 @@ class Attention(nn.Module):
         if ctx.is_prefill:
             if ctx.cu_seqlens_q is None:
                 raise ValueError("cu_seqlens_q must be provided for varlen attention")
-            o = flash_attention_prefill(q, k, v, ctx.cu_seqlens_q, scale, self.num_heads, self.num_kv_heads,
-                                        self.head_dim)
+            if ctx.block_tables is not None and ctx.cu_seqlens_k is not None and has_cache:
+                # some sequence has a cached prefix: attend through the paged cache (this step's K/V are in it)
+                o = flash_attention_prefill_paged(q, k_cache, v_cache, ctx.cu_seqlens_q, ctx.cu_seqlens_k,
+                                                  ctx.block_tables, scale, self.num_heads, self.num_kv_heads,
+                                                  self.head_dim)
+            else:
+                o = flash_attention_prefill(q, k, v, ctx.cu_seqlens_q, scale, self.num_heads, self.num_kv_heads,
+                                            self.head_dim)
         else:
             o = paged_attention_decode(q, k_cache, v_cache, ctx.block_tables, ctx.context_lens, scale,
                                        self.num_heads, self.num_kv_heads, self.head_dim, k_cache.shape[1],

@@ -166,3 +166,37 @@ def qk_norm_rope(x, positions, cos_table, sin_table, gamma, eps, dtype):
     cos, sin = cos_table[positions][:, None, :], sin_table[positions][:, None, :]
     x1, x2 = n.chunk(2, dim=-1)
     return torch.cat([x1 * cos - x2 * sin, x1 * sin + x2 * cos], dim=-1).to(dtype)
+
+
+# --------------------------------------------------------------------------
+# prefill with a cached prefix (keys and values read from the paged cache)
+# --------------------------------------------------------------------------
+def flash_attention_prefill_paged(q, k_cache, v_cache, cu_seqlens_q, cu_seqlens_k, block_tables, scale, num_heads,
+                                  num_kv_heads, head_dim):
+    """Sequence s: q rows [cu_q[s], cu_q[s+1]) are its LAST queries; it has cu_k[s+1]-cu_k[s] keys at cache rows
+    block_tables[s, j // bs] * bs + j % bs.  Query i sits at position keys - queries + i and attends to keys at
+    positions <= its own: the rows that the full-sequence causal attention (flash_attention_prefill above,
+    src/myvllm/layers/attention.py:111-209) would produce for those positions.  The reference never computes
+    this case (its kernel ignores cu_seqlens_k), so the pin is that equivalence, checked in the tests."""
+    qf = q.to(torch.float32)
+    kc, vc = k_cache.to(torch.float32), v_cache.to(torch.float32)
+    bs = k_cache.shape[1]
+    group = num_heads // num_kv_heads
+    out = torch.zeros_like(qf)
+    cq, ck = [int(x) for x in cu_seqlens_q], [int(x) for x in cu_seqlens_k]
+    for s in range(len(cq) - 1):
+        nq, nk = cq[s + 1] - cq[s], ck[s + 1] - ck[s]
+        if nq <= 0:
+            continue
+        pos = torch.arange(nk)
+        rows = block_tables[s, pos // bs].to(torch.int64) * bs + pos % bs
+        k = kc.reshape(-1, num_kv_heads, head_dim)[rows]
+        v = vc.reshape(-1, num_kv_heads, head_dim)[rows]
+        qs = qf[cq[s]:cq[s + 1]].reshape(nq, num_kv_heads, group, head_dim)
+        scores = torch.einsum("ikgd,jkd->kgij", qs, k) * scale
+        qpos = (nk - nq) + torch.arange(nq)
+        mask = pos[None, :] <= qpos[:, None]
+        scores = scores.masked_fill(~mask, float("-inf"))
+        o = torch.einsum("kgij,jkd->ikgd", torch.softmax(scores, dim=-1), v)
+        out[cq[s]:cq[s + 1]] = o.reshape(nq, num_heads, head_dim)
+    return out
