@@ -24,7 +24,8 @@ class LLMEngine:
             max_num_seqs=self.model_runner.max_num_seqs,
             max_num_batched_tokens=_cfg(config, "max_num_batched_tokens", default=1024),
             num_blocks=num_blocks, block_size=self.block_size, eos=config.get("eos", -1),
-            num_slots=self.model_runner.max_num_seqs)
+            num_slots=self.model_runner.max_num_seqs,
+            prefix_caching=config.get("enable_prefix_caching", False))
         self.stats = dict(prefill_tokens=0, decode_tokens=0, prefill_s=0.0, decode_s=0.0, steps=0)
 
     def add_prompt(self, token_ids, sampling_params: SamplingParams = None):
@@ -42,7 +43,7 @@ class LLMEngine:
         tokens = self.model_runner.run(seqs, is_prefill)
         dt = time.perf_counter() - t0
         self.scheduler.postprocess(seqs, tokens)
-        n = sum(len(s) - 1 for s in seqs) if is_prefill else len(seqs)
+        n = sum(len(s) - 1 - s.num_cached_tokens for s in seqs) if is_prefill else len(seqs)
         key = "prefill" if is_prefill else "decode"
         self.stats[key + "_tokens"] += n
         self.stats[key + "_s"] += dt

@@ -126,8 +126,15 @@ class ModelRunner:
         input_ids = torch.tensor(ids, dtype=torch.int64).pin_memory().to(self.device, non_blocking=True)
         meta = self.state.build_prefill([s.slot for s in seqs], [len(s) for s in seqs],
                                         [s.num_cached_tokens for s in seqs])
+        tables = None
+        if any(s.num_cached_tokens for s in seqs):
+            # a prefix hit: attention must read keys through the block tables (the reference sets them too,
+            # model_runner.py:209-215, but its kernel never uses them)
+            slots = torch.tensor([s.slot for s in seqs], dtype=torch.int64).pin_memory().to(self.device,
+                                                                                             non_blocking=True)
+            tables = self.state.tables.index_select(0, slots)
         set_context(True, meta["cu_seqlens_q"], meta["cu_seqlens_k"], meta["max_seqlen_q"], meta["max_seqlen_k"],
-                    meta["slot_mapping"], None, None, positions=meta["positions"],
+                    meta["slot_mapping"], None, tables, positions=meta["positions"],
                     last_token_index=meta["last_token_index"])
         return input_ids
 

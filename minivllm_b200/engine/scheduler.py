@@ -10,10 +10,11 @@ from .sequence import Sequence, SequenceStatus
 
 
 class Scheduler:
-    def __init__(self, max_num_seqs, max_num_batched_tokens, num_blocks, block_size, eos, num_slots=None):
+    def __init__(self, max_num_seqs, max_num_batched_tokens, num_blocks, block_size, eos, num_slots=None,
+                 prefix_caching=False):
         self.max_num_seqs = max_num_seqs
         self.max_num_batched_tokens = max_num_batched_tokens
-        self.block_manager = BlockManager(num_blocks, block_size, num_slots or max_num_seqs)
+        self.block_manager = BlockManager(num_blocks, block_size, num_slots or max_num_seqs, prefix_caching)
         self.eos = eos
         self.waiting: deque[Sequence] = deque()
         self.running: deque[Sequence] = deque()

@@ -63,3 +63,21 @@ def test_temperature_sampling_runs_in_graph_mode():
     out = eng.generate(_prompts(4), SamplingParams(temperature=0.6, max_tokens=8, ignore_eos=True))
     assert all(len(t) == 8 and all(0 <= x < CONFIG["vocab_size"] for x in t) for t in out["token_ids"])
     eng.exit()
+
+
+def test_prefix_caching_keeps_streams_and_hits_the_cache():
+    """Prompts that share their first 48 tokens (3 blocks of 16): with the prefix cache on, later requests
+    feed only their uncached suffix through the paged prefill kernel; greedy streams must not change."""
+    torch.cuda.set_device(0)
+    g = torch.Generator().manual_seed(3)
+    shared = torch.randint(0, CONFIG["vocab_size"], (48,), generator=g).tolist()
+    prompts = [shared + torch.randint(0, CONFIG["vocab_size"], (n,), generator=g).tolist() for n in (5, 17, 1, 30)]
+    sp = SamplingParams(temperature=0.0, max_tokens=20, ignore_eos=True)
+    outs = {}
+    for caching in (False, True):
+        eng = LLMEngine(dict(CONFIG, enforce_eager=False, enable_prefix_caching=caching, max_num_seqs=2))
+        outs[caching] = eng.generate(prompts, sp)["token_ids"]
+        hits = eng.scheduler.block_manager.cached_hits
+        eng.exit()
+        assert (hits > 0) == caching
+    assert outs[True] == outs[False]

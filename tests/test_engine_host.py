@@ -117,3 +117,31 @@ def test_tensor_parallel_sharding_matches_single_rank_on_gloo(tmp_path):
     outs = [p.communicate(timeout=240)[0] for p in procs]
     assert all(p.returncode == 0 for p in procs), "\n".join(outs)
     assert "TP_MAXERR" in outs[0]
+
+
+def test_prefix_cache_reuses_full_blocks_but_never_the_last_one():
+    bm = BlockManager(num_blocks=16, block_size=4, num_slots=4, prefix_caching=True)
+    a = Sequence(list(range(10)), block_size=4)          # blocks [0-3], [4-7], [8,9]
+    bm.allocate(a)
+    assert a.num_cached_tokens == 0 and len(a.block_table) == 3
+    b = Sequence(list(range(8)) + [99, 98, 97], block_size=4)   # same first two blocks
+    bm.allocate(b)
+    assert b.num_cached_tokens == 8 and b.block_table[:2] == a.block_table[:2] and b.block_table[2] != a.block_table[2]
+    c = Sequence(list(range(8)), block_size=4)           # exactly the shared blocks: the last one is recomputed
+    bm.allocate(c)
+    assert c.num_cached_tokens == 4 and c.block_table[0] == a.block_table[0] and c.block_table[1] != a.block_table[1]
+    # shared blocks survive the release of one owner and are revived from the free list
+    bm.deallocate(a); bm.deallocate(b); bm.deallocate(c)
+    assert len(bm.free_blocks) == 16
+    d = Sequence(list(range(8)) + [5], block_size=4)
+    bm.allocate(d)
+    assert d.num_cached_tokens == 8
+    # a block filled during decode becomes reusable once complete
+    e = Sequence([7, 7, 7], block_size=4)
+    bm.allocate(e)
+    for tok in (1, 2):
+        e.append_token(tok)
+        bm.append(e)            # 5 tokens: the step that writes position 4 finds block 0 complete
+    f = Sequence([7, 7, 7, 1, 2, 3], block_size=4)
+    bm.allocate(f)
+    assert f.num_cached_tokens == 4 and f.block_table[0] == e.block_table[0]
