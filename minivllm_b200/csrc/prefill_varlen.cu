@@ -63,20 +63,24 @@ struct PrefillParams {
 };
 
 enum { BAR_Q = 0, BAR_KFULL = 1, BAR_KEMPTY = 3, BAR_VFULL = 5, BAR_VEMPTY = 7, BAR_SFULL = 9, BAR_PREADY = 11,
-       BAR_ODONE = 13, BAR_COUNT = 15 };
+       BAR_ODONE = 13, BAR_SPARE = 15, BAR_COUNT = 16 };
 
 #ifdef MV_PF_TRACE
 // Timeline probe (debug builds only, -DMV_PF_TRACE): one thread of each role of ONE CTA writes clock64()
 // stamps per KV step, so that the phases of the pipeline can be read off without a profiler.
 __device__ long long* g_pf_trace = nullptr;
 __device__ int g_pf_trace_cta = -1;
-#define PF_STAMP(role, j, k)                                                                           \
-  do {                                                                                                 \
-    if (g_pf_trace && static_cast<int>(blockIdx.x) == g_pf_trace_cta && blockIdx.y == 0 && (j) < 32)  \
-      g_pf_trace[((role) * 32 + (j)) * 8 + (k)] = clock64();                                          \
+// pf_tr is read once per thread at kernel start: a stamp is then one predicated store, cheap enough not to
+// distort the warp it measures.
+#define PF_STAMP(role, j, k)                                                      \
+  do {                                                                            \
+    if (pf_tr && (j) < 32) pf_tr[((role) * 32 + (j)) * 8 + (k)] = clock64();      \
   } while (0)
+#define PF_TRACE_INIT() \
+  long long* const pf_tr = (static_cast<int>(blockIdx.x) == g_pf_trace_cta && blockIdx.y == 0) ? g_pf_trace : nullptr
 #else
 #define PF_STAMP(role, j, k) do {} while (0)
+#define PF_TRACE_INIT() do {} while (0)
 #endif
 
 __device__ __forceinline__ float ex2(float x) {
@@ -98,6 +102,7 @@ prefill_varlen_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
   __shared__ int s_sticky;
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  PF_TRACE_INIT();
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   const uint32_t q_smem = smem_base;                                  // [head 2][half 2][128][128B]
   const uint32_t k_smem = q_smem + 2 * kPfTileBytes;                  // [stage][half][128][128B]
@@ -182,6 +187,7 @@ prefill_varlen_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
       tc::mbar_init(bar(BAR_PREADY + t), 128);
       tc::mbar_init(bar(BAR_ODONE + t), 1);
     }
+    tc::mbar_init(bar(BAR_SPARE), 1);   // takes commits that nobody waits for
     tc::mbar_fence_init();
   }
   if (warp == 8) {
@@ -253,37 +259,20 @@ prefill_varlen_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
         const uint32_t q_lo0 = tc::desc_lo(q_smem, 16);
         const uint32_t k_lo0 = tc::desc_lo(k_smem, 16);
         const uint32_t v_lo0 = tc::desc_lo(v_smem, kPfHalfBytes);
-        auto issue_qk = [&](int t, int s) {
-          const uint32_t q_lo = q_lo0 + t * (kPfTileBytes >> 4);
-          const uint32_t k_lo = k_lo0 + s * (kPfTileBytes >> 4);
-          const uint32_t s_tmem = tmem + t * 128;
-#pragma unroll
-          for (int h = 0; h < 2; ++h)
-#pragma unroll
-            for (int ks = 0; ks < 4; ++ks) {
-              const uint32_t off = (h * kPfHalfBytes + ks * 32) >> 4;
-              if (tc::elect_one())
-                tc::mma_ss(s_tmem, tc::desc64(q_lo + off, desc_hi), tc::desc64(k_lo + off, desc_hi), idesc_qk,
-                           (h | ks) != 0);
-            }
+        auto issue_qk = [&](int t, int s) {   // S_t = Q_t K(stage s)^T, then commit to SFULL[t]
+          tc::mma_ss_k128_commit(tmem + t * 128, tc::desc64(q_lo0 + t * (kPfTileBytes >> 4), desc_hi),
+                                 tc::desc64(k_lo0 + s * (kPfTileBytes >> 4), desc_hi), idesc_qk, bar(BAR_SFULL + t));
         };
-        auto issue_pv = [&](int t, int s, bool accum, int p_col) {
-          const uint32_t v_lo = v_lo0 + s * (kPfTileBytes >> 4);
-          const uint32_t p_tmem = tmem + t * 128 + p_col, o_tmem = tmem + 256 + t * 128;
-#pragma unroll
-          for (int ks = 0; ks < 8; ++ks)
-            if (tc::elect_one())
-              tc::mma_ts(o_tmem, p_tmem + ks * 8, tc::desc64(v_lo + ks * (2048 >> 4), desc_hi), idesc_pv,
-                         accum || ks != 0);
+        // O_t (+)= P_t V(stage s); commit to `commit_bar` (ODONE[t] after the last PV of the step)
+        auto issue_pv = [&](int t, int s, bool accum, int p_col, uint32_t commit_bar) {
+          tc::mma_ts_k128_commit(tmem + 256 + t * 128, tmem + t * 128 + p_col,
+                                 tc::desc64(v_lo0 + s * (kPfTileBytes >> 4), desc_hi), idesc_pv, accum, commit_bar);
         };
         tc::mbar_wait(bar(BAR_Q), 0, abort_flag, p.error_word, 3);
         tc::mbar_wait(bar(BAR_KFULL + 0), 0, abort_flag, p.error_word, 4);
         tc::fence_after_sync();
-        for (int t = 0; t < nt; ++t) {
-          issue_qk(t, 0);
-          if (tc::elect_one()) tc::mma_commit(bar(BAR_SFULL + t));
-        }
-        if (tc::elect_one()) tc::mma_commit(bar(BAR_KEMPTY + 0));  // K stage 0 is free once QK(0) of both heads has run
+        for (int t = 0; t < nt; ++t) issue_qk(t, 0);
+        tc::commit_elected(bar(BAR_KEMPTY + 0), 0, false);  // K stage 0 is free once QK(0) of both heads has run
         for (int j = 0; j < n_kv; ++j) {
           const int s = j % kPfStages;
           const uint32_t ph = (j / kPfStages) & 1;
@@ -295,26 +284,18 @@ prefill_varlen_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
             tc::mbar_wait(bar(BAR_PREADY + t), j & 1, abort_flag, p.error_word, 7);
             tc::fence_after_sync();
             if (lane == 0) PF_STAMP(2 + t, j, 0);
-            issue_pv(t, s, j > 0, 0);
-            if (split_p) issue_pv(t, s, true, 64);   // residue of P, see the softmax warps
-            if (tc::elect_one()) tc::mma_commit(bar(BAR_ODONE + t));
-            if (lane == 0) PF_STAMP(2 + t, j, 1);
-#ifdef MV_PF_TRACE_SERIAL
-            tc::mbar_wait(bar(BAR_ODONE + t), j & 1, abort_flag, p.error_word, 11);   // probe: PV alone, issue to completion
-            if (lane == 0) PF_STAMP(2 + t, j, 3);
-#endif
-            if (more) {
-              issue_qk(t, s1);
-              if (tc::elect_one()) tc::mma_commit(bar(BAR_SFULL + t));
+            if (split_p) {   // P, then its rounding residue (see the softmax warps); the first commit is a spare arrival-free one
+              issue_pv(t, s, j > 0, 0, bar(BAR_SPARE));
+              issue_pv(t, s, true, 64, bar(BAR_ODONE + t));
+            } else {
+              issue_pv(t, s, j > 0, 0, bar(BAR_ODONE + t));
             }
+            if (lane == 0) PF_STAMP(2 + t, j, 1);
+            if (more) issue_qk(t, s1);
             if (lane == 0) PF_STAMP(2 + t, j, 2);
-#ifdef MV_PF_TRACE_SERIAL
-            if (more) tc::mbar_wait(bar(BAR_SFULL + t), (j + 1) & 1, abort_flag, p.error_word, 12);  // probe: QK alone
-            if (lane == 0) PF_STAMP(2 + t, j, 4);
-#endif
           }
-          if (tc::elect_one()) tc::mma_commit(bar(BAR_VEMPTY + s));     // both PV(j) issued -> V stage free when they have run
-          if (more) if (tc::elect_one()) tc::mma_commit(bar(BAR_KEMPTY + s1));
+          // V stage s is free when both PV(j) have run, K stage s1 when both QK(j+1) have
+          tc::commit_elected(bar(BAR_VEMPTY + s), bar(BAR_KEMPTY + s1), more);
         }
       }
     }

@@ -179,6 +179,76 @@ __device__ __forceinline__ void mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_
       "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
       ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(acc) : "memory");
 }
+// Eight MMAs over K = 128 and the commit that follows them, issued by one elected lane of a CONVERGED warp in a
+// single predicated sequence: the issuing warp shares its scheduler with busy softmax warps, so every
+// instruction it does not execute shortens the critical path.  Descriptor offsets (16-byte units) are added
+// to the low word; shared-memory addresses stay below 256 KB, so the add never carries out of the address field.
+//   D[tmem] (+)= A[smem] * B[smem]; A and B are K-major tiles of two 64-column halves, `half_off` apart.
+__device__ __forceinline__ void mma_ss_k128_commit(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                                   uint32_t commit_bar) {
+  asm volatile(
+      "{\n\t.reg .pred pe, pt, pf;\n\t.reg .b64 da, db;\n\t"
+      "elect.sync _|pe, 0xffffffff;\n\t"
+      "setp.eq.u32 pt, %3, %3;\n\t"
+      "setp.ne.u32 pf, %3, %3;\n\t"
+      "@pe tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, pf;\n\t"
+      "add.s64 da, %1, 2;\n\tadd.s64 db, %2, 2;\n\t"
+      "@pe tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %3, pt;\n\t"
+      "add.s64 da, %1, 4;\n\tadd.s64 db, %2, 4;\n\t"
+      "@pe tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %3, pt;\n\t"
+      "add.s64 da, %1, 6;\n\tadd.s64 db, %2, 6;\n\t"
+      "@pe tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %3, pt;\n\t"
+      "add.s64 da, %1, 1024;\n\tadd.s64 db, %2, 1024;\n\t"
+      "@pe tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %3, pt;\n\t"
+      "add.s64 da, %1, 1026;\n\tadd.s64 db, %2, 1026;\n\t"
+      "@pe tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %3, pt;\n\t"
+      "add.s64 da, %1, 1028;\n\tadd.s64 db, %2, 1028;\n\t"
+      "@pe tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %3, pt;\n\t"
+      "add.s64 da, %1, 1030;\n\tadd.s64 db, %2, 1030;\n\t"
+      "@pe tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %3, pt;\n\t"
+      "@pe tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%4];\n\t}"
+      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(commit_bar) : "memory");
+}
+//   D[tmem] (+)= A[tmem] * B[smem]; A holds two 16-bit values per column (8 columns per MMA), B is an MN-major
+//   tile whose 16-row slices are 2048 bytes apart.
+__device__ __forceinline__ void mma_ts_k128_commit(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc,
+                                                   bool accum, uint32_t commit_bar) {
+  const uint32_t acc = accum ? 1u : 0u;
+  asm volatile(
+      "{\n\t.reg .pred pe, pt, pf;\n\t.reg .b64 db;\n\t.reg .b32 ta;\n\t"
+      "elect.sync _|pe, 0xffffffff;\n\t"
+      "setp.eq.u32 pt, %3, %3;\n\t"
+      "setp.ne.u32 pf, %4, 0;\n\t"
+      "@pe tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, pf;\n\t"
+      "add.u32 ta, %1, 8;\n\tadd.s64 db, %2, 128;\n\t"
+      "@pe tcgen05.mma.cta_group::1.kind::f16 [%0], [ta], db, %3, pt;\n\t"
+      "add.u32 ta, %1, 16;\n\tadd.s64 db, %2, 256;\n\t"
+      "@pe tcgen05.mma.cta_group::1.kind::f16 [%0], [ta], db, %3, pt;\n\t"
+      "add.u32 ta, %1, 24;\n\tadd.s64 db, %2, 384;\n\t"
+      "@pe tcgen05.mma.cta_group::1.kind::f16 [%0], [ta], db, %3, pt;\n\t"
+      "add.u32 ta, %1, 32;\n\tadd.s64 db, %2, 512;\n\t"
+      "@pe tcgen05.mma.cta_group::1.kind::f16 [%0], [ta], db, %3, pt;\n\t"
+      "add.u32 ta, %1, 40;\n\tadd.s64 db, %2, 640;\n\t"
+      "@pe tcgen05.mma.cta_group::1.kind::f16 [%0], [ta], db, %3, pt;\n\t"
+      "add.u32 ta, %1, 48;\n\tadd.s64 db, %2, 768;\n\t"
+      "@pe tcgen05.mma.cta_group::1.kind::f16 [%0], [ta], db, %3, pt;\n\t"
+      "add.u32 ta, %1, 56;\n\tadd.s64 db, %2, 896;\n\t"
+      "@pe tcgen05.mma.cta_group::1.kind::f16 [%0], [ta], db, %3, pt;\n\t"
+      "@pe tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%5];\n\t}"
+      ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(acc), "r"(commit_bar) : "memory");
+}
+// One or two commits by the elected lane of a converged warp.
+__device__ __forceinline__ void commit_elected(uint32_t bar_a, uint32_t bar_b, bool both) {
+  const uint32_t two = both ? 1u : 0u;
+  asm volatile(
+      "{\n\t.reg .pred pe, p2;\n\t"
+      "elect.sync _|pe, 0xffffffff;\n\t"
+      "setp.ne.u32 p2, %2, 0;\n\t"
+      "and.pred p2, p2, pe;\n\t"
+      "@pe tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n\t"
+      "@p2 tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%1];\n\t}"
+      ::"r"(bar_a), "r"(bar_b), "r"(two) : "memory");
+}
 // The mbarrier gets one arrival when every MMA issued so far by this thread has completed.
 __device__ __forceinline__ void mma_commit(uint32_t bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
