@@ -46,6 +46,11 @@ __device__ __forceinline__ uint4 ld_stream16(const void* p) {
 __device__ __forceinline__ void st_global16(void* p, const uint4& v) {
   asm volatile("st.global.v4.u32 [%0], {%1,%2,%3,%4};" ::"l"(p), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
 }
+// 32-byte store (a whole sector per thread); the address must be 32-byte aligned.
+__device__ __forceinline__ void st_global32(void* p, const uint4& a, const uint4& b) {
+  asm volatile("st.global.v8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"l"(p), "r"(a.x), "r"(a.y), "r"(a.z), "r"(a.w),
+               "r"(b.x), "r"(b.y), "r"(b.z), "r"(b.w) : "memory");
+}
 __device__ __forceinline__ void st_global8(void* p, const uint2& v) {
   asm volatile("st.global.v2.u32 [%0], {%1,%2};" ::"l"(p), "r"(v.x), "r"(v.y) : "memory");
 }

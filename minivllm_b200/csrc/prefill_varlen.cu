@@ -48,6 +48,7 @@ constexpr float kRescaleThreshold = 8.f;                    // log2 units
 struct PrefillParams {
   void* out;
   int64_t out_stride_tok;  // elements
+  int out_align32;         // output rows start on 32-byte boundaries
   const int32_t* cu_seqlens;
   int num_seqs, num_heads, num_kv_heads, group, pairs;  // pairs = ceil(group / 2)
   float scale_log2;
@@ -240,6 +241,15 @@ prefill_varlen_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
           tc::mbar_wait(bar(BAR_VEMPTY + s), ph, abort_flag, p.error_word, 2);
           tc::mbar_expect_tx(bar(BAR_VFULL + s), kPfTileBytes);
           load_kv_tile(&tmap_v, v_smem + s * kPfTileBytes, j, bar(BAR_VFULL + s));
+        }
+        // After an abort nobody may be left to consume the loads already issued: give them time to land before
+        // the CTA (and its shared memory) goes away.  A full barrier completes its phase when its bytes arrive.
+        if (*abort_flag) {
+          tc::mbar_wait_timed(bar(BAR_Q), 0);
+          for (int j = max(n_kv - kPfStages, 0); j < n_kv; ++j) {
+            tc::mbar_wait_timed(bar(BAR_KFULL + j % kPfStages), (j / kPfStages) & 1);
+            tc::mbar_wait_timed(bar(BAR_VFULL + j % kPfStages), (j / kPfStages) & 1);
+          }
         }
       }
     } else if (warp == 9) {
@@ -456,14 +466,24 @@ prefill_varlen_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
         tc::tmem_ld32(o_addr + c * 32, ov);
         tc::wait_ld();
         if (store) {
-#pragma unroll
-          for (int i = 0; i < 4; ++i) {
+          auto packed = [&](int i) {   // eight outputs, columns 32c + 8i ..
             uint4 w;
             w.x = pack2<T>(__uint_as_float(ov[8 * i + 0]) * inv_l, __uint_as_float(ov[8 * i + 1]) * inv_l);
             w.y = pack2<T>(__uint_as_float(ov[8 * i + 2]) * inv_l, __uint_as_float(ov[8 * i + 3]) * inv_l);
             w.z = pack2<T>(__uint_as_float(ov[8 * i + 4]) * inv_l, __uint_as_float(ov[8 * i + 5]) * inv_l);
             w.w = pack2<T>(__uint_as_float(ov[8 * i + 6]) * inv_l, __uint_as_float(ov[8 * i + 7]) * inv_l);
-            st_global16(orow + c * 32 + i * 8, w);
+            return w;
+          };
+          // a thread writes its own 256-byte row: whole 32-byte sectors when the output allows it (a warp-wide
+          // store touches 32 different lines either way, so fewer, larger requests is what counts)
+#pragma unroll
+          for (int i = 0; i < 4; i += 2) {
+            if (p.out_align32) {
+              st_global32(orow + c * 32 + i * 8, packed(i), packed(i + 1));
+            } else {
+              st_global16(orow + c * 32 + i * 8, packed(i));
+              st_global16(orow + c * 32 + i * 8 + 8, packed(i + 1));
+            }
           }
         }
       }
@@ -586,6 +606,7 @@ extern "C" int mv_prefill_varlen(void* out, const void* q, const void* k, const 
   PrefillParams p;
   p.out = out;
   p.out_stride_tok = static_cast<int64_t>(num_heads) * head_dim;
+  p.out_align32 = (reinterpret_cast<uintptr_t>(out) & 31u) == 0;   // rows are 256-byte multiples apart
   p.cu_seqlens = cu_seqlens;
   p.num_seqs = num_seqs;
   p.num_heads = num_heads;
@@ -642,6 +663,7 @@ extern "C" int mv_prefill_paged(void* out, const void* q, int64_t q_stride_tok, 
   PrefillParams p;
   p.out = out;
   p.out_stride_tok = static_cast<int64_t>(num_heads) * head_dim;
+  p.out_align32 = (reinterpret_cast<uintptr_t>(out) & 31u) == 0;   // rows are 256-byte multiples apart
   p.cu_seqlens = cu_seqlens_q;
   p.num_seqs = num_seqs;
   p.num_heads = num_heads;

@@ -59,6 +59,15 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
     if (mbar_try_wait(bar, parity)) return true;
   return mbar_wait_slow(bar, parity, abort_flag, error_word, where);
 }
+// Wait bounded by time alone (2 ms), for draining copies in flight after an abort.
+__device__ __forceinline__ bool mbar_wait_timed(uint32_t bar, uint32_t parity) {
+  const unsigned long long t0 = global_ns();
+  do {
+    for (int i = 0; i < 64; ++i)
+      if (mbar_try_wait(bar, parity)) return true;
+  } while (global_ns() - t0 < 2000000ull);
+  return false;
+}
 
 // --------------------------------------------------------------------- TMA ---
 // 3-D tiled load global -> shared, completion counted in bytes on an mbarrier.

@@ -61,6 +61,29 @@ def test_prefill_shape_sweep(dtype, kw):
     _close(_gpu(d, dtype), _oracle(d, dtype), dtype)
 
 
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_prefill_more_tiles_than_sms_with_odd_group(dtype):
+    """Several hundred (tile, head pair) units with a group of three heads (a pair plus a single head): every
+    SM works through many units, of different lengths and with and without a second head."""
+    d = synth.prefill_inputs(seed=61, num_seqs=14, len_lo=250, len_hi=900, num_heads=6, num_kv_heads=2, head_dim=128)
+    _close(_gpu(d, dtype), _oracle(d, dtype), dtype)
+
+
+def test_prefill_batch_of_many_short_sequences():
+    """More sequences than the kernel keeps a tile table for in shared memory, some of them empty."""
+    g = torch.Generator().manual_seed(62)
+    lens = torch.randint(0, 40, (1100,), generator=g)
+    lens[::97] = 0
+    lens[5] = 300
+    cu = torch.zeros(1101, dtype=torch.int32)
+    cu[1:] = torch.cumsum(lens, 0)
+    total = int(cu[-1])
+    d = dict(q=torch.randn(total, 2, 128, generator=g), k=torch.randn(total, 1, 128, generator=g),
+             v=torch.randn(total, 1, 128, generator=g), cu_seqlens=cu, scale=128 ** -0.5, num_heads=2, num_kv_heads=1,
+             head_dim=128)
+    _close(_gpu(d, torch.float16), _oracle(d, torch.float16), torch.float16)
+
+
 def test_prefill_long_sequence_and_large_logits():
     """2,048-token sequences (16 KV tiles), then a scale that makes the running maximum jump by far more
     than the lazy-rescale threshold, so O in tensor memory is rescaled."""
