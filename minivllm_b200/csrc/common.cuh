@@ -27,6 +27,8 @@ template <> struct Elem<__half> {
   static __device__ __forceinline__ __half from_f(float x) { return __float2half_rn(x); }
   static __device__ __forceinline__ float2 to_f2(__half2 x) { return __half22float2(x); }
   static __device__ __forceinline__ __half2 from_f2(float a, float b) { return __floats2half2_rn(a, b); }
+  static __device__ __forceinline__ __half2 absmax2(__half2 m, __half2 x) { return __hmax2(m, __habs2(x)); }
+  static __device__ __forceinline__ float hmax_f(__half2 m) { return __half2float(__hmax(__low2half(m), __high2half(m))); }
 };
 template <> struct Elem<__nv_bfloat16> {
   using T2 = __nv_bfloat162;
@@ -34,6 +36,10 @@ template <> struct Elem<__nv_bfloat16> {
   static __device__ __forceinline__ __nv_bfloat16 from_f(float x) { return __float2bfloat16_rn(x); }
   static __device__ __forceinline__ float2 to_f2(__nv_bfloat162 x) { return __bfloat1622float2(x); }
   static __device__ __forceinline__ __nv_bfloat162 from_f2(float a, float b) { return __floats2bfloat162_rn(a, b); }
+  static __device__ __forceinline__ __nv_bfloat162 absmax2(__nv_bfloat162 m, __nv_bfloat162 x) { return __hmax2(m, __habs2(x)); }
+  static __device__ __forceinline__ float hmax_f(__nv_bfloat162 m) {
+    return __bfloat162float(__hmax(__low2bfloat16(m), __high2bfloat16(m)));
+  }
 };
 
 // 16-byte streaming load that does not allocate in L1 (data is used once).
@@ -61,6 +67,22 @@ __device__ __forceinline__ float fast_exp2(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
+}
+
+// Blackwell packed fp32 pairs: one issue slot for two lanes of work.
+__device__ __forceinline__ float2 mul_f32x2(float2 a, float2 b) {
+  float2 d;
+  asm("mul.rn.f32x2 %0, %1, %2;"
+      : "=l"(reinterpret_cast<unsigned long long&>(d))
+      : "l"(reinterpret_cast<unsigned long long&>(a)), "l"(reinterpret_cast<unsigned long long&>(b)));
+  return d;
+}
+__device__ __forceinline__ float2 add_f32x2(float2 a, float2 b) {
+  float2 d;
+  asm("add.rn.f32x2 %0, %1, %2;"
+      : "=l"(reinterpret_cast<unsigned long long&>(d))
+      : "l"(reinterpret_cast<unsigned long long&>(a)), "l"(reinterpret_cast<unsigned long long&>(b)));
+  return d;
 }
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {

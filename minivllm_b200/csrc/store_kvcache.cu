@@ -80,19 +80,17 @@ __device__ __noinline__ int quant_exact(float x, float s) {
 // eight when the scale is not a normal fp16 number (then |x/s| may exceed
 // 127.5 and needs the clamp).  One IEEE division and one IEEE reciprocal per
 // head row (lane 0 of the group), none per element.
+// The kernel is bound by instruction issue, not by HBM, so the per-element work is packed: the row maximum is
+// taken on the 16-bit pairs as they come (|x| and max are exact in any format), products, roundings and the
+// near-tie distances run on fp32 pairs.  Lanes of an invalid token hold zeros: amax = 0, inv = 0, codes 0,
+// and nothing is stored.
 template <typename T, int GROUP>
-__device__ __forceinline__ void quant_chunk(const uint4& raw, bool live, uint2& codes, __half& scale16) {
-  float x[8];
-  const typename Elem<T>::T2* p2 = reinterpret_cast<const typename Elem<T>::T2*>(&raw);
-#pragma unroll
-  for (int j = 0; j < 4; ++j) {
-    const float2 f = Elem<T>::to_f2(p2[j]);
-    x[2 * j] = live ? f.x : 0.f;
-    x[2 * j + 1] = live ? f.y : 0.f;
-  }
-  float amax = 0.f;
-#pragma unroll
-  for (int j = 0; j < 8; ++j) amax = fmaxf(amax, fabsf(x[j]));
+__device__ __forceinline__ void quant_chunk(const uint4& raw, uint2& codes, __half& scale16) {
+  using T2 = typename Elem<T>::T2;
+  const T2* p2 = reinterpret_cast<const T2*>(&raw);
+  T2 m2 = Elem<T>::absmax2(Elem<T>::absmax2(Elem<T>::from_f2(0.f, 0.f), p2[0]), p2[1]);
+  m2 = Elem<T>::absmax2(Elem<T>::absmax2(m2, p2[2]), p2[3]);
+  float amax = Elem<T>::hmax_f(m2);
 #pragma unroll
   for (int off = GROUP / 2; off > 0; off >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, off));
   // amax is the same in every lane of the group, so every lane computes the scale itself (no leader branch):
@@ -110,23 +108,34 @@ __device__ __forceinline__ void quant_chunk(const uint4& raw, bool live, uint2& 
 
   constexpr float kMagic = 12582912.f;  // 1.5 * 2^23: adding it rounds to nearest-even integer
   constexpr float kNearTie = 0.4999f;   // product error is < 127 * 2^-21 = 6e-5 (approximate reciprocal + rounding): anything closer to k + 1/2 is re-done
+  const float2 inv2 = make_float2(inv, inv), magic2 = make_float2(kMagic, kMagic), nmagic2 = make_float2(-kMagic, -kMagic);
+  float2 x2[4];
   uint32_t t[8];
-  float dist[8], worst = 0.f;
+  float worst = 0.f;
 #pragma unroll
-  for (int j = 0; j < 8; ++j) {
-    const float y = x[j] * inv;
-    const float tj = y + kMagic;
-    t[j] = __float_as_uint(tj);
-    dist[j] = fabsf(y - (tj - kMagic));
-    worst = fmaxf(worst, dist[j]);
+  for (int j = 0; j < 4; ++j) {
+    x2[j] = Elem<T>::to_f2(p2[j]);
+    const float2 y = mul_f32x2(x2[j], inv2);
+    const float2 tj = add_f32x2(y, magic2);                       // low byte of each word = the code
+    const float2 rounded = add_f32x2(tj, nmagic2);
+    const float2 d = add_f32x2(y, make_float2(-rounded.x, -rounded.y));   // distance from the rounded value
+    t[2 * j] = __float_as_uint(tj.x);
+    t[2 * j + 1] = __float_as_uint(tj.y);
+    worst = fmaxf(worst, fmaxf(fabsf(d.x), fabsf(d.y)));
   }
   if (inv == 0.f) {
 #pragma unroll
-    for (int j = 0; j < 8; ++j) t[j] = static_cast<uint32_t>(quant_exact(x[j], s));
+    for (int j = 0; j < 4; ++j) {
+      t[2 * j] = static_cast<uint32_t>(quant_exact(x2[j].x, s));
+      t[2 * j + 1] = static_cast<uint32_t>(quant_exact(x2[j].y, s));
+    }
   } else if (worst > kNearTie) {
 #pragma unroll
-    for (int j = 0; j < 8; ++j)
-      if (dist[j] > kNearTie) t[j] = static_cast<uint32_t>(quant_exact(x[j], s));
+    for (int j = 0; j < 8; ++j) {
+      const float x = (j & 1) ? x2[j >> 1].y : x2[j >> 1].x;
+      const float y = x * inv;
+      if (fabsf(y - ((y + kMagic) - kMagic)) > kNearTie) t[j] = static_cast<uint32_t>(quant_exact(x, s));
+    }
   }
   // low bytes of t[0..7] -> two words
   uint32_t a01, a23;
@@ -152,14 +161,16 @@ store_kv_quant_kernel(const uint4* __restrict__ key, const uint4* __restrict__ v
   const int64_t stride = static_cast<int64_t>(gridDim.x) * kStoreThreads;
   const int64_t rounds = (total_chunks + stride - 1) / stride;
   int64_t i = static_cast<int64_t>(blockIdx.x) * kStoreThreads + threadIdx.x;
+  // (token, chunk within the row) of chunk i, advanced by the stride each round: one division per thread
+  int64_t t = i / chunks_per_row;
+  uint32_t c = static_cast<uint32_t>(i - t * chunks_per_row);
+  const int64_t t_step = stride / chunks_per_row;
+  const uint32_t c_step = static_cast<uint32_t>(stride - t_step * chunks_per_row);
   for (int64_t r = 0; r < rounds; ++r, i += stride) {
     bool live = false;
-    int64_t t = 0, slot = -1;
-    uint32_t c = 0;
+    int64_t slot = -1;
     uint4 kraw = make_uint4(0, 0, 0, 0), vraw = make_uint4(0, 0, 0, 0);
     if (i < total_chunks) {
-      t = i / chunks_per_row;
-      c = static_cast<uint32_t>(i - t * chunks_per_row);
       slot = __ldg(slot_mapping + t);
       live = slot >= 0 && slot < num_slots;
       if (live) {
@@ -169,8 +180,8 @@ store_kv_quant_kernel(const uint4* __restrict__ key, const uint4* __restrict__ v
     }
     uint2 kc, vc;
     __half ks, vs;
-    quant_chunk<T, GROUP>(kraw, live, kc, ks);
-    quant_chunk<T, GROUP>(vraw, live, vc, vs);
+    quant_chunk<T, GROUP>(kraw, kc, ks);
+    quant_chunk<T, GROUP>(vraw, vc, vs);
     if (live) {
       const int64_t dst = slot * chunks_per_row + c;  // 8-byte units of the int8 row
       st_global8(k_codes + dst, kc);
@@ -180,6 +191,12 @@ store_kv_quant_kernel(const uint4* __restrict__ key, const uint4* __restrict__ v
         k_scale[sidx] = ks;
         v_scale[sidx] = vs;
       }
+    }
+    t += t_step;
+    c += c_step;
+    if (c >= chunks_per_row) {
+      c -= chunks_per_row;
+      ++t;
     }
   }
 }
