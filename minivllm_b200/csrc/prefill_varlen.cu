@@ -28,6 +28,7 @@
 #include <cuda.h>
 #include "tcgen05.cuh"
 #include "mma.cuh"
+#include <atomic>
 #include <type_traits>
 
 namespace mv {
@@ -49,6 +50,8 @@ struct PrefillParams {
   void* out;
   int64_t out_stride_tok;  // elements
   int out_align32;         // output rows start on 32-byte boundaries
+  int inject;              // test hook, normally 0.  1: head A of tile 0 withholds its first "P ready" arrival,
+                           // so that the MMA warp's bounded wait runs out and the abort path is exercised
   const int32_t* cu_seqlens;
   int num_seqs, num_heads, num_kv_heads, group, pairs;  // pairs = ceil(group / 2)
   float scale_log2;
@@ -64,7 +67,7 @@ struct PrefillParams {
 };
 
 enum { BAR_Q = 0, BAR_KFULL = 1, BAR_KEMPTY = 3, BAR_VFULL = 5, BAR_VEMPTY = 7, BAR_SFULL = 9, BAR_PREADY = 11,
-       BAR_ODONE = 13, BAR_SPARE = 15, BAR_COUNT = 16 };
+       BAR_ODONE = 13, BAR_SPARE = 15, BAR_DRAIN = 16, BAR_COUNT = 17 };
 
 #ifdef MV_PF_TRACE
 // Timeline probe (debug builds only, -DMV_PF_TRACE): one thread of each role of ONE CTA writes clock64()
@@ -189,6 +192,7 @@ prefill_varlen_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
       tc::mbar_init(bar(BAR_ODONE + t), 1);
     }
     tc::mbar_init(bar(BAR_SPARE), 1);   // takes commits that nobody waits for
+    tc::mbar_init(bar(BAR_DRAIN), 1);
     tc::mbar_fence_init();
   }
   if (warp == 8) {
@@ -306,6 +310,11 @@ prefill_varlen_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
           }
           // V stage s is free when both PV(j) have run, K stage s1 when both QK(j+1) have
           tc::commit_elected(bar(BAR_VEMPTY + s), bar(BAR_KEMPTY + s1), more);
+        }
+        // After an abort nobody waits for the last MMAs: they must have run before tensor memory is freed.
+        if (*abort_flag) {
+          tc::commit_elected(bar(BAR_DRAIN), 0, false);
+          tc::mbar_wait_timed(bar(BAR_DRAIN), 0);
         }
       }
     }
@@ -449,7 +458,7 @@ prefill_varlen_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
         if (tid == 0) PF_STAMP(0, j, 3);
         tc::wait_st();
         tc::fence_before_sync();
-        tc::mbar_arrive(bar(BAR_PREADY + t));
+        if (!(p.inject == 1 && t == 0 && j == 0 && blockIdx.x == 0 && blockIdx.y == 0)) tc::mbar_arrive(bar(BAR_PREADY + t));
         if (tid == 0) PF_STAMP(0, j, 4);
         if (tid == 128) PF_STAMP(1, j, 4);
       }
@@ -545,6 +554,8 @@ extern "C" int mv_debug_prefill_trace(long long* buffer, int cta) {
 #endif
 
 namespace mv {
+static std::atomic<int> g_prefill_inject{0};
+
 static int launch_prefill(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, PrefillParams& p,
                           int64_t total_tokens, int num_seqs, int num_kv_heads, int dtype, void* stream) {
   // Upper bound on the number of query tiles, from shapes only: no host sync.
@@ -552,6 +563,7 @@ static int launch_prefill(const CUtensorMap& tq, const CUtensorMap& tk, const CU
   if (max_tiles > 0x7fffffffLL || static_cast<int64_t>(num_kv_heads) * p.pairs > 65535)
     return fail(MV_ERR_LIMIT, "prefill: grid too large");
   const dim3 grid(static_cast<unsigned>(max_tiles), static_cast<unsigned>(num_kv_heads * p.pairs));
+  p.inject = g_prefill_inject.exchange(0);   // one launch only
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   static bool attr_done[64][2] = {};
   int dev = 0;
@@ -574,6 +586,14 @@ static int launch_prefill(const CUtensorMap& tq, const CUtensorMap& tk, const CU
   return check_launch("prefill_varlen_kernel");
 }
 }  // namespace mv
+
+// Test hook: the NEXT prefill launch of this process runs with the given fault injected on the host side of
+// the launch (see PrefillParams::inject).  Nothing faults or hangs: a bounded wait runs out, the error word is
+// set and the kernel returns.
+extern "C" int mv_debug_prefill_inject(int mode) {
+  mv::g_prefill_inject.store(mode);
+  return MV_OK;
+}
 
 extern "C" int mv_prefill_varlen(void* out, const void* q, const void* k, const void* v, int64_t q_stride_tok,
                                  int64_t k_stride_tok, int64_t v_stride_tok, const int32_t* cu_seqlens, int num_seqs,

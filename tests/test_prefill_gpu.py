@@ -5,7 +5,9 @@ import numpy as np
 import pytest
 import torch
 
-from minivllm_b200 import synth
+import ctypes
+
+from minivllm_b200 import _cabi, synth
 from minivllm_b200.layers import attention as A
 from oracle import attention_oracle as oracle
 
@@ -131,3 +133,48 @@ def test_prefill_rejects_head_dim_64():
     with pytest.raises(ValueError):
         A.flash_attention_prefill(d["q"].half().to(DEV), d["k"].half().to(DEV), d["v"].half().to(DEV),
                                   d["cu_seqlens"].to(DEV), 0.1, 2, 1, 64)
+
+
+def _call_c_abi(d, dtype, out, error_word):
+    q, k, v = (d[n].to(dtype).to(DEV) for n in ("q", "k", "v"))
+    cu = d["cu_seqlens"].to(DEV)
+    h, kvh, hd = d["num_heads"], d["num_kv_heads"], d["head_dim"]
+    rc = _cabi.lib().mv_prefill_varlen(out.data_ptr(), q.data_ptr(), k.data_ptr(), v.data_ptr(), h * hd, kvh * hd,
+                                       kvh * hd, cu.data_ptr(), cu.numel() - 1, q.shape[0], h, kvh, hd,
+                                       float(d["scale"]), error_word.data_ptr(), _cabi.dtype_code(dtype),
+                                       _cabi.stream_ptr())
+    torch.cuda.synchronize()
+    return rc
+
+
+def test_prefill_with_error_word_set_returns_at_once():
+    """A wait that ran out leaves the error word set; until the caller clears it every launch is a no-op
+    (its CTAs return before touching tensor memory or the output)."""
+    d = synth.prefill_inputs(seed=64, num_seqs=2, len_lo=100, len_hi=300, num_heads=4, num_kv_heads=2, head_dim=128)
+    dtype = torch.float16
+    out = torch.full(tuple(d["q"].shape), 7.0, dtype=dtype, device=DEV)
+    word = torch.full((1,), 0x105, dtype=torch.int32, device=DEV)
+    assert _call_c_abi(d, dtype, out, word) == 0
+    assert int(word.item()) == 0x105 and bool((out == 7.0).all())
+    word.zero_()
+    assert _call_c_abi(d, dtype, out, word) == 0
+    assert int(word.item()) == 0
+    _close(out.float().cpu(), _oracle(d, dtype), dtype)
+
+
+def test_prefill_wait_that_runs_out_is_reported():
+    """Failure detection without a fault: one arrival on an mbarrier is withheld (host-side injection for ONE
+    launch), the MMA warp's bounded wait runs out after 200 ms, the kernel sets the error word, frees its tensor
+    memory and returns; the context stays usable and the next launch is clean."""
+    d = synth.prefill_inputs(seed=65, num_seqs=1, len_lo=128, len_hi=128, num_heads=2, num_kv_heads=1, head_dim=128)
+    dtype = torch.float16
+    out = torch.zeros(tuple(d["q"].shape), dtype=dtype, device=DEV)
+    word = torch.zeros(1, dtype=torch.int32, device=DEV)
+    assert _cabi.lib().mv_debug_prefill_inject(ctypes.c_int(1)) == 0
+    assert _call_c_abi(d, dtype, out, word) == 0          # the launch itself succeeds
+    code = int(word.item())
+    assert code >> 8 == 1, f"error word {code:#x}"         # 0x100 + the number of the wait that gave up
+    word.zero_()
+    assert _call_c_abi(d, dtype, out, word) == 0          # the injection was for one launch only
+    assert int(word.item()) == 0
+    _close(out.float().cpu(), _oracle(d, dtype), dtype)
