@@ -244,6 +244,29 @@ int mv_qk_norm_rope_store(const void* qkv, int64_t qkv_stride_tok,
                           int num_kv_heads, int head_dim, int dtype,
                           void* stream);
 
+/*
+ * Greedy sampling tail.  mv_argmax_rows reduces each row of a logits matrix
+ * (rows, cols), row stride in elements, to one signed 64-bit key: high word =
+ * the maximum logit in an integer form whose order is the float order (NaN
+ * above +inf, as torch.argmax treats it), low word = 2^32-1 minus
+ * (index_offset + column).  The larger key is the larger logit and, between
+ * equal logits, the lower index, so vocabulary shards merge by an integer MAX
+ * (e.g. an all-reduce of 8 bytes per row) -- mv_argmax_decode takes the
+ * largest of `shards` keys per row, keys laid out (shards, rows), and writes
+ * the token ids.  keys or tokens of mv_argmax_rows may be NULL; with tokens
+ * set the decoded ids of this shard alone are written too (single-GPU path,
+ * one launch).  Rows that start on 16-byte boundaries (aligned base, stride a
+ * multiple of 8 elements) are read with 16-byte loads, others element-wise.
+ * Replaces the gather of full-vocabulary logits to rank 0 and the argmax on
+ * them: src/myvllm/layers/embedding_head.py:56-77 (ParallelLMHead.forward)
+ * and src/myvllm/layers/sampler.py:15-19 in its greedy limit.
+ */
+int mv_argmax_rows(const void* logits, int64_t row_stride, int64_t rows,
+                   int64_t cols, int64_t index_offset, int64_t* keys,
+                   int64_t* tokens, int dtype, void* stream);
+int mv_argmax_decode(const int64_t* keys, int shards, int64_t rows,
+                     int64_t* tokens, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -29,6 +29,9 @@ template <> struct Elem<__half> {
   static __device__ __forceinline__ __half2 from_f2(float a, float b) { return __floats2half2_rn(a, b); }
   static __device__ __forceinline__ __half2 absmax2(__half2 m, __half2 x) { return __hmax2(m, __habs2(x)); }
   static __device__ __forceinline__ float hmax_f(__half2 m) { return __half2float(__hmax(__low2half(m), __high2half(m))); }
+  // maxima that propagate NaN (a NaN anywhere in the inputs gives NaN)
+  static __device__ __forceinline__ __half2 max2_nan(__half2 a, __half2 b) { return __hmax2_nan(a, b); }
+  static __device__ __forceinline__ float hmax_nan_f(__half2 m) { return __half2float(__hmax_nan(__low2half(m), __high2half(m))); }
 };
 template <> struct Elem<__nv_bfloat16> {
   using T2 = __nv_bfloat162;
@@ -39,6 +42,10 @@ template <> struct Elem<__nv_bfloat16> {
   static __device__ __forceinline__ __nv_bfloat162 absmax2(__nv_bfloat162 m, __nv_bfloat162 x) { return __hmax2(m, __habs2(x)); }
   static __device__ __forceinline__ float hmax_f(__nv_bfloat162 m) {
     return __bfloat162float(__hmax(__low2bfloat16(m), __high2bfloat16(m)));
+  }
+  static __device__ __forceinline__ __nv_bfloat162 max2_nan(__nv_bfloat162 a, __nv_bfloat162 b) { return __hmax2_nan(a, b); }
+  static __device__ __forceinline__ float hmax_nan_f(__nv_bfloat162 m) {
+    return __bfloat162float(__hmax_nan(__low2bfloat16(m), __high2bfloat16(m)));
   }
 };
 

@@ -23,6 +23,7 @@ import torch.distributed as dist
 
 from ..utils.context import get_context, reset_context, set_context
 from .metadata import SequenceStateTable
+from ..layers.sampler import greedy_tokens
 from .qwen3 import Qwen3Config, Qwen3ForCausalLM
 
 
@@ -166,17 +167,29 @@ class ModelRunner:
 
     # ---------------------------------------------------------------- sampling ---
     def sample(self, logits, temperatures=None):
-        """Greedy argmax, or the reference's exponential-race draw (src/myvllm/layers/sampler.py:15-19)."""
-        if self.greedy or temperatures is None:
-            return logits.argmax(dim=-1)
+        """The reference's exponential-race draw (src/myvllm/layers/sampler.py:15-19) on full-vocabulary logits."""
         probs = torch.softmax(logits.float() / temperatures.unsqueeze(-1), dim=-1)
         noise = torch.empty_like(probs).exponential_(1).clamp_min_(1e-10)
         return probs.div_(noise).argmax(dim=-1)
 
+    def next_tokens(self, hidden, temperatures=None):
+        """hidden states -> sampled token ids.  Greedy: each rank multiplies by its slice of the vocabulary only
+        and the ranks merge one 64-bit key per row (layers/sampler.py) instead of gathering or replicating the
+        151,936-wide logits; with a temperature every rank computes the full logits and draws with the same seed."""
+        if self.greedy or temperatures is None:
+            vocab = self.model.lm_head.shape[0]
+            shard = self.world_size > 1 and vocab % self.world_size == 0
+            if shard:
+                logits = self.model.compute_logits(hidden, (self.rank, self.world_size))
+                return greedy_tokens(logits, self.rank * (vocab // self.world_size), None, self.world_size)
+            return greedy_tokens(self.model.compute_logits(hidden))
+        return self.sample(self.model.compute_logits(hidden), temperatures)
+
     # --------------------------------------------------------------------- run ---
     @torch.inference_mode()
     def run_model(self, input_ids, is_prefill):
-        return self.model.compute_logits(self.model(input_ids))
+        """Hidden states of the rows that get a next token (last token of each sequence in prefill)."""
+        return self.model(input_ids)
 
     @torch.inference_mode()
     def run(self, seqs, is_prefill):
@@ -186,13 +199,13 @@ class ModelRunner:
                 self.device, non_blocking=True)
         if is_prefill:
             input_ids = self.prepare_prefill(seqs)
-            tokens = self.sample(self.run_model(input_ids, True), temps)
+            tokens = self.next_tokens(self.run_model(input_ids, True), temps)
             slots = torch.tensor([s.slot for s in seqs], dtype=torch.int64).pin_memory().to(self.device,
                                                                                              non_blocking=True)
             self.state.last_token.index_copy_(0, slots, tokens)
         elif self.enforce_eager or not self.graphs:
             input_ids, slots_buf = self.prepare_decode(seqs)
-            tokens = self.sample(self.run_model(input_ids, False), temps)
+            tokens = self.next_tokens(self.run_model(input_ids, False), temps)
             self.state.last_token.index_copy_(0, slots_buf.long(), tokens)
         else:
             tokens = self._replay(seqs, temps)
@@ -206,8 +219,7 @@ class ModelRunner:
         bufs = {k: t[:bp] for k, t in v["bufs"].items()}
         self.state.build_decode(v["slots"][:bp], v["n_active"], bufs)
         self._set_decode_context(bufs)
-        logits = self.model.compute_logits(self.model(bufs["input_ids"]))
-        tokens = self.sample(logits, None if self.greedy else v["temps"][:bp])
+        tokens = self.next_tokens(self.model(bufs["input_ids"]), None if self.greedy else v["temps"][:bp])
         v["tokens"][:bp].copy_(tokens)
         self.state.last_token.index_copy_(0, v["slots"][:bp].long(), tokens)
 

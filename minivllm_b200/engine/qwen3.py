@@ -176,9 +176,16 @@ class Qwen3ForCausalLM(nn.Module):
             x, residual = layer(x, residual, cos, sin, (self.rope_cos, self.rope_sin))
         return F.rms_norm(residual + x, (x.shape[-1],), self.final_norm_w, RMS_EPS)
 
-    def compute_logits(self, hidden):
-        """Prefill keeps the last token of every sequence (Context.last_token_index); decode keeps all rows."""
+    def compute_logits(self, hidden, vocab_shard=None):
+        """Prefill keeps the last token of every sequence (Context.last_token_index); decode keeps all rows.
+        vocab_shard = (rank, size): only that slice of the vocabulary rows of the (replicated) head, i.e.
+        logits (rows, vocab / size) whose column 0 is token rank * vocab / size."""
         ctx = get_context()
         if ctx.is_prefill and ctx.last_token_index is not None:
             hidden = hidden[ctx.last_token_index]
-        return F.linear(hidden, self.lm_head)
+        w = self.lm_head
+        if vocab_shard is not None:
+            rank, size = vocab_shard
+            per = w.shape[0] // size
+            w = w[rank * per:(rank + 1) * per]
+        return F.linear(hidden, w)

@@ -1,6 +1,6 @@
 """Small, self-contained runs of each kernel for profilers:
 
-    python -m minivllm_b200.profile_cases {store|store_int8|decode_int8|prefill|pre_attention} [launches]
+    python -m minivllm_b200.profile_cases {store|store_int8|decode_int8|prefill|pre_attention|argmax} [launches]
 
 Each case holds well under 2 GB on the device, is larger than L2 where DRAM
 figures matter, launches its kernel a handful of times and prints the CUDA
@@ -62,6 +62,19 @@ def case_decode_int8(n):
     print(f"paged decode int8: {ms * 1e3:.1f} us/launch, algorithmic {nbytes / 1e6:.1f} MB, {nbytes / ms / 1e6:.0f} GB/s")
 
 
+def case_argmax(n):
+    """Greedy tail on decode-sized logits: 512 rows x 151,936 columns bf16 (the full vocabulary of one rank at TP=1)."""
+    from minivllm_b200.layers import sampler as S
+    g = torch.Generator().manual_seed(5)
+    x = torch.randn(512, 151936, generator=g).to(torch.bfloat16).to(DEV)
+    ms = _timed(lambda: S.argmax_rows(x, want_keys=False, want_tokens=True), n)
+    ref = _timed(lambda: x.argmax(dim=-1), n)
+    same = bool((S.argmax_rows(x, want_keys=False, want_tokens=True)[1] == x.float().argmax(dim=-1)).all())
+    nbytes = x.numel() * 2 + 512 * 8
+    print(f"argmax_rows 512x151936 bf16: {ms * 1e3:.1f} us/launch, algorithmic {nbytes / 1e6:.1f} MB, "
+          f"{nbytes / ms / 1e6:.0f} GB/s; torch.argmax {ref * 1e3:.1f} us; same tokens {same}")
+
+
 def case_prefill(n):
     p = synth.prefill_inputs()
     bf = torch.bfloat16
@@ -94,7 +107,8 @@ def main():
     case = sys.argv[1] if len(sys.argv) > 1 else "store"
     n = int(sys.argv[2]) if len(sys.argv) > 2 else 3
     {"store": lambda: case_store(n), "store_int8": lambda: case_store(n, True), "decode_int8": lambda: case_decode_int8(n),
-     "prefill": lambda: case_prefill(n), "pre_attention": lambda: case_pre_attention(n)}[case]()
+     "prefill": lambda: case_prefill(n), "pre_attention": lambda: case_pre_attention(n),
+     "argmax": lambda: case_argmax(n)}[case]()
 
 
 if __name__ == "__main__":
