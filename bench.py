@@ -326,12 +326,14 @@ class EngineWorkload:
 
     def launches_per_step(self):
         """Kernels of this library launched by one generate(): per model step and layer one store_kvcache and
-        one attention call (decode = split-K kernel + combine), plus the metadata kernels of the step."""
+        one attention call (decode = split-K kernel + combine), plus the metadata kernels of the step and its
+        greedy sampling tail (row argmax; under tensor parallelism also the key decode after the all-reduce)."""
         s = self.last_stats
         layers = self.cfg["num_layers"]
         decode_steps = self.out_tokens_per_step // len(self.prompts) - 1
         prefill_waves = s["steps"] - decode_steps
-        return decode_steps * (layers * 3 + 1) + prefill_waves * (layers * 2 + 2)
+        tail = (2 if self.world > 1 else 1) if self.cfg.get("greedy", False) else 0
+        return decode_steps * (layers * 3 + 1 + tail) + prefill_waves * (layers * 2 + 2 + tail)
 
     def decode_probe(self, iters=36):
         """Times paged_attention_decode with CUDA events on the engine's own KV pool at the shape of the

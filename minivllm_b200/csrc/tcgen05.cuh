@@ -129,16 +129,7 @@ __device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32
 //   bits 32..45  stride byte offset >> 4   (distance between 8-row groups)
 //   bits 46..47  version = 1
 //   bits 61..63  layout = 2 (SWIZZLE_128B)
-__device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
-  uint64_t d = 0;
-  d |= static_cast<uint64_t>((saddr & 0x3ffffu) >> 4);
-  d |= static_cast<uint64_t>((lbo_bytes >> 4) & 0x3fffu) << 16;
-  d |= static_cast<uint64_t>((sbo_bytes >> 4) & 0x3fffu) << 32;
-  d |= 1ull << 46;
-  d |= 2ull << 61;
-  return d;
-}
-// The same descriptor split into its two 32-bit words, so that an issuing thread builds the fixed part once
+// The descriptor is kept as its two 32-bit words, so that an issuing thread builds the fixed part once
 // and only adds offsets (16-byte units, no carry out of the 14-bit field) to the low word.
 constexpr uint32_t kDescHiSw128Sbo1024 = (1024u >> 4) | (1u << 14) | (2u << 29);
 __device__ __forceinline__ uint32_t desc_lo(uint32_t saddr, uint32_t lbo_bytes) {
@@ -159,40 +150,15 @@ __host__ __device__ constexpr uint32_t instr_desc_f16(uint32_t fmt_a, uint32_t f
          | ((b_mn_major ? 1u : 0u) << 16)
          | ((n >> 3) << 17) | ((m >> 4) << 24);
 }
-// One lane of a converged warp.  The MMA issuer runs its whole loop with all 32 lanes converged and lets the
-// elected lane execute the tcgen05 instructions: their operands travel through the uniform datapath, and a
-// warp that has diverged on `lane == 0` pays ~90-140 cycles per MMA to get them there (measured).
-__device__ __forceinline__ bool elect_one() {
-  uint32_t is_leader;
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "elect.sync _|p, 0xffffffff;\n\t"
-      "selp.b32 %0, 1, 0, p;\n\t}"
-      : "=r"(is_leader));
-  return is_leader != 0;
-}
-
-// D[tmem] (+)= A[smem] * B[smem]
-__device__ __forceinline__ void mma_ss(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, bool accum) {
-  const uint32_t acc = accum ? 1u : 0u;
-  asm volatile(
-      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(acc) : "memory");
-}
-// D[tmem] (+)= A[tmem] * B[smem]
-__device__ __forceinline__ void mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, bool accum) {
-  const uint32_t acc = accum ? 1u : 0u;
-  asm volatile(
-      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
-      ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(acc) : "memory");
-}
+// The MMA issuer runs its whole loop with all 32 lanes converged and lets ONE elected lane execute the tcgen05
+// instructions (elect.sync inside the sequences below): their operands travel through the uniform datapath, and
+// a warp that has diverged on `lane == 0` pays ~90-140 cycles per MMA to get them there (measured).
 // Eight MMAs over K = 128 and the commit that follows them, issued by one elected lane of a CONVERGED warp in a
 // single predicated sequence: the issuing warp shares its scheduler with busy softmax warps, so every
 // instruction it does not execute shortens the critical path.  Descriptor offsets (16-byte units) are added
 // to the low word; shared-memory addresses stay below 256 KB, so the add never carries out of the address field.
-//   D[tmem] (+)= A[smem] * B[smem]; A and B are K-major tiles of two 64-column halves, `half_off` apart.
+//   D[tmem] (+)= A[smem] * B[smem]; A and B are K-major 128-row tiles stored as two 64-column halves
+//   16 KB apart (1024 descriptor units); four K = 16 steps of 32 bytes (2 units) in each half.
 __device__ __forceinline__ void mma_ss_k128_commit(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
                                                    uint32_t commit_bar) {
   asm volatile(
@@ -258,11 +224,6 @@ __device__ __forceinline__ void commit_elected(uint32_t bar_a, uint32_t bar_b, b
       "@p2 tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%1];\n\t}"
       ::"r"(bar_a), "r"(bar_b), "r"(two) : "memory");
 }
-// The mbarrier gets one arrival when every MMA issued so far by this thread has completed.
-__device__ __forceinline__ void mma_commit(uint32_t bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
-}
-
 // ------------------------------------------------------- softmax arithmetic ---
 // Blackwell packed fp32 pairs (one issue slot for two lanes of work) and the three-input max.
 __device__ __forceinline__ float2 fma2(float2 a, float2 b, float2 c) {
