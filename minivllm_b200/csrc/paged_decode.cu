@@ -9,6 +9,9 @@
 //     on the device from sum(context_lens) so that the machine is filled
 //     whatever the batch looks like; the grid is persistent and depends on
 //     shapes only (graph-capturable).  Every CTA recomputes the same plan.
+//     The chunk length only fixes how many items a sequence gets; its tokens
+//     are then spread evenly over them (items of similar length: CTAs take
+//     items in a fixed stride).
 //   * a CTA is 4 independent warps.  Each warp streams its own 16-token tiles
 //     of K and V through a private cp.async ring in shared memory (XOR-swizzled
 //     16-byte chunks, conflict-free for ldmatrix), so the main loop has no

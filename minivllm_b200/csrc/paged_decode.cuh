@@ -14,7 +14,8 @@ constexpr int kTileTok = 16;                    // tokens per warp tile
 constexpr int kCtaTok = kTileTok * kDecWarps;   // tokens per CTA step
 constexpr int kChunkMax = 2048;                 // longest KV chunk of one work item
 constexpr int kDecCtasPerSM = 2;
-constexpr int kDecWaves = 2;                    // work items aimed at per resident CTA
+constexpr int kDecWaves = 2;                    // work items aimed at per resident CTA (8 and 16 measured slower:
+                                                // every item refills its ring and merges its warps)
 constexpr float kNegBig = -1e30f;               // finite "minus infinity" for running maxima
 
 struct DecodeParams {
@@ -126,8 +127,13 @@ __device__ __forceinline__ DecodeItem find_item(const DecodeParams& p, const int
   DecodeItem it;
   it.b = lo;
   it.nsplit = s_start[lo + 1] - s_start[lo];
-  it.tok_begin = (item - s_start[lo]) * chunk;
-  it.tok_end = min(load_ctx(p, lo), it.tok_begin + chunk);
+  // The sequence's tokens are spread evenly over its items (in whole CTA steps) instead of full chunks plus a
+  // short remainder: CTAs take items in a fixed stride, so items of similar length mean a similar load.
+  const int ctx = load_ctx(p, lo);
+  int per = (ctx + it.nsplit - 1) / it.nsplit;
+  per = ((per + kCtaTok - 1) / kCtaTok) * kCtaTok;   // <= chunk, which is a multiple of kCtaTok
+  it.tok_begin = (item - s_start[lo]) * per;
+  it.tok_end = min(ctx, it.tok_begin + per);
   return it;
 }
 
