@@ -38,9 +38,16 @@ struct DecodeSmem {
   static constexpr int kMergeStride = D + 8;                       // floats per merged row
   static constexpr int kMergeBytes = kDecWarps * 16 * kMergeStride * 4 + kDecWarps * 16 * 2 * 4;
   static_assert(kMergeBytes <= kRingBytes, "merge buffer must fit in the ring");
+  // streaming variant: a merge buffer of its own, for groups of up to kStreamRows query heads
+  static constexpr int kStreamRows = 4;
+  static constexpr int kStreamMergeBytes = kDecWarps * kStreamRows * kMergeStride * 4 + kDecWarps * kStreamRows * 2 * 4;
 };
 
-template <typename T, int D>
+// kStream = false: every work item fills its rings from empty and the merge buffer reuses the ring memory.
+// kStream = true (groups of up to four query heads, one row tile): the merge buffer has memory of its own and a
+// warp's tiles form ONE stream across the work items of its CTA -- the loads run two tiles ahead of the MMAs
+// also across an item boundary, so the next item's first tiles arrive during the merge of the current one.
+template <typename T, int D, bool kStream>
 __global__ void __launch_bounds__(kDecThreads, kDecCtasPerSM)
 paged_decode_kernel(const DecodeParams p) {
   using S = DecodeSmem<T, D>;
@@ -54,7 +61,7 @@ paged_decode_kernel(const DecodeParams p) {
   extern __shared__ __align__(128) unsigned char smem[];
   __shared__ long long s_red[kDecWarps];
   __shared__ uint32_t s_mask[kDecWarps][kDecStages];
-  int* s_start = reinterpret_cast<int*>(smem + S::kRingBytes);
+  int* s_start = reinterpret_cast<int*>(smem + S::kRingBytes + (kStream ? S::kStreamMergeBytes : 0));
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int g = lane >> 2, t = lane & 3;
@@ -73,56 +80,96 @@ paged_decode_kernel(const DecodeParams p) {
   const T* vc = static_cast<const T*>(p.v_cache);
   const int bs = p.block_size;
 
+  // What a warp needs to know of a work item.
+  struct Item {
+    int b, nsplit, tok_begin, tok_end, kvh, mt, item, my_tiles;
+    const int32_t* table;
+  };
+  auto load_item = [&](long long w, Item& it) -> bool {
+    if (w >= total_work) return false;
+    it.item = static_cast<int>(w / ydim);
+    const int y = static_cast<int>(w - static_cast<long long>(it.item) * ydim);
+    it.kvh = y / p.mtiles;
+    it.mt = y - it.kvh * p.mtiles;
+    const DecodeItem di = find_item(p, s_start, it.item, chunk);
+    it.b = di.b; it.nsplit = di.nsplit; it.tok_begin = di.tok_begin; it.tok_end = di.tok_end;
+    it.table = p.block_tables + static_cast<int64_t>(di.b) * p.bt_stride;
+    // tiles of this warp: tokens tok_begin + (i*kDecWarps + warp)*16
+    const int span = di.tok_end - di.tok_begin;
+    const int cta_tiles = span > 0 ? (span + kTileTok - 1) / kTileTok : 0;
+    it.my_tiles = cta_tiles > warp ? (cta_tiles - warp + kDecWarps - 1) / kDecWarps : 0;
+    return true;
+  };
+  // ring stage <- tile i of this warp within item `it` (no commit)
+  auto issue_tile = [&](const Item& it, int i, int stage) {
+    const int tok0 = it.tok_begin + (i * kDecWarps + warp) * kTileTok;
+    const int blk0 = tok0 / bs, off0 = tok0 - blk0 * bs;
+    // lane r (r < 16) resolves row r; others mirror it
+    const int r_me = lane & 15;
+    int off = off0 + r_me, blk = blk0;
+    while (off >= bs) { off -= bs; ++blk; }
+    int slot = -1;
+    if (tok0 + r_me < it.tok_end) {
+      const int pb = __ldg(it.table + blk);
+      if (pb >= 0 && pb < p.num_blocks) slot = pb * bs + off;
+    }
+    const uint32_t live = __ballot_sync(0xffffffffu, slot >= 0) & 0xffffu;
+    if (lane == 0) s_mask[warp][stage] = live;
+    const uint32_t kdst = ring + stage * S::kStageBytes;
+    const uint32_t vdst = kdst + S::kTileBytes;
+    const int c = lane % CPR, r0 = lane / CPR;
+#pragma unroll
+    for (int li = 0; li < LOAD_ITERS; ++li) {
+      const int r = r0 + li * RPI;
+      const int s = __shfl_sync(0xffffffffu, slot, r);
+      const int64_t eoff = s >= 0 ? (static_cast<int64_t>(s) * p.num_kv_heads + it.kvh) * D + c * 8 : 0;
+      const uint32_t doff = r * S::kRowBytes + ((c ^ (r & 7)) << 4);
+      cp_async16(kdst + doff, kc + eoff, s >= 0 ? 16 : 0);
+      cp_async16(vdst + doff, vc + eoff, s >= 0 ? 16 : 0);
+    }
+  };
+  // kStream: the load side walks the warp's tile stream on its own, two ring slots ahead of the MMAs.  Every
+  // slot is one cp.async group (empty once the stream has ended), so "at most one group pending" always
+  // means that the slot about to be consumed has landed.
+  long long load_w = blockIdx.x;
+  Item load_it;
+  bool load_valid = false;
+  int load_tile = 0, load_slot = 0, use_slot = 0;
+  auto issue_next = [&]() {
+    while (load_valid && load_tile >= load_it.my_tiles) {
+      load_w += gridDim.x;
+      load_valid = load_item(load_w, load_it);
+      load_tile = 0;
+    }
+    if (load_valid) {
+      issue_tile(load_it, load_tile, load_slot % kDecStages);
+      ++load_tile;
+    }
+    cp_async_commit();
+    ++load_slot;
+  };
+  if constexpr (kStream) {
+    load_valid = load_item(load_w, load_it);
+#pragma unroll
+    for (int i = 0; i < kDecStages - 1; ++i) issue_next();
+  }
+
   for (long long w = blockIdx.x; w < total_work; w += gridDim.x) {
-    const int item = static_cast<int>(w / ydim);
-    const int y = static_cast<int>(w - static_cast<long long>(item) * ydim);
-    const int kvh = y / p.mtiles, mt = y - kvh * p.mtiles;
-    const DecodeItem di = find_item(p, s_start, item, chunk);
-    const int b = di.b, nsplit = di.nsplit, tok_begin = di.tok_begin, tok_end = di.tok_end;
-    const int32_t* table = p.block_tables + static_cast<int64_t>(b) * p.bt_stride;
+    Item cur;
+    load_item(w, cur);
+    const int item = cur.item, kvh = cur.kvh, mt = cur.mt, b = cur.b, nsplit = cur.nsplit, my_tiles = cur.my_tiles;
     const int rows_valid = min(16, p.group - mt * 16);
     const int h0 = kvh * p.group + mt * 16;
 
-    // tiles of this warp: tokens tok_begin + (i*kDecWarps + warp)*16
-    const int span = tok_end - tok_begin;
-    const int cta_tiles = span > 0 ? (span + kTileTok - 1) / kTileTok : 0;
-    const int my_tiles = cta_tiles > warp ? (cta_tiles - warp + kDecWarps - 1) / kDecWarps : 0;
-
-    auto issue = [&](int i) {
-      // stage i % kDecStages <- tile i of this warp (or nothing past the end)
-      if (i < my_tiles) {
-        const int stage = i % kDecStages;
-        const int tok0 = tok_begin + (i * kDecWarps + warp) * kTileTok;
-        const int blk0 = tok0 / bs, off0 = tok0 - blk0 * bs;
-        // lane r (r < 16) resolves row r; others mirror it
-        const int r_me = lane & 15;
-        int off = off0 + r_me, blk = blk0;
-        while (off >= bs) { off -= bs; ++blk; }
-        int slot = -1;
-        if (tok0 + r_me < tok_end) {
-          const int pb = __ldg(table + blk);
-          if (pb >= 0 && pb < p.num_blocks) slot = pb * bs + off;
-        }
-        const uint32_t live = __ballot_sync(0xffffffffu, slot >= 0) & 0xffffu;
-        if (lane == 0) s_mask[warp][stage] = live;
-        const uint32_t kdst = ring + stage * S::kStageBytes;
-        const uint32_t vdst = kdst + S::kTileBytes;
-        const int c = lane % CPR, r0 = lane / CPR;
-#pragma unroll
-        for (int it = 0; it < LOAD_ITERS; ++it) {
-          const int r = r0 + it * RPI;
-          const int s = __shfl_sync(0xffffffffu, slot, r);
-          const int64_t eoff = s >= 0 ? (static_cast<int64_t>(s) * p.num_kv_heads + kvh) * D + c * 8 : 0;
-          const uint32_t doff = r * S::kRowBytes + ((c ^ (r & 7)) << 4);
-          cp_async16(kdst + doff, kc + eoff, s >= 0 ? 16 : 0);
-          cp_async16(vdst + doff, vc + eoff, s >= 0 ? 16 : 0);
-        }
-      }
+    auto issue = [&](int i) {   // not streaming: stage i % kDecStages <- tile i of this item (or nothing past its end)
+      if (i < my_tiles) issue_tile(cur, i, i % kDecStages);
       cp_async_commit();
     };
 
+    if constexpr (!kStream) {
 #pragma unroll
-    for (int i = 0; i < kDecStages - 1; ++i) issue(i);
+      for (int i = 0; i < kDecStages - 1; ++i) issue(i);
+    }
 
     // Q fragments: rows g and g+8 of the 16-row tile, zero past the group.
     uint32_t qa[KSTEPS][4];
@@ -148,7 +195,7 @@ paged_decode_kernel(const DecodeParams p) {
     for (int i = 0; i < my_tiles; ++i) {
       cp_async_wait<kDecStages - 2>();
       __syncwarp();
-      const int stage = i % kDecStages;
+      const int stage = (kStream ? use_slot : i) % kDecStages;
       const uint32_t kbase = ring + stage * S::kStageBytes;
       const uint32_t vbase = kbase + S::kTileBytes;
       const uint32_t live = s_mask[warp][stage];
@@ -169,7 +216,7 @@ paged_decode_kernel(const DecodeParams p) {
       }
       // Issue the next tile now: its slot was released at the end of the
       // previous iteration, and the loads overlap the softmax below.
-      issue(i + kDecStages - 1);
+      if constexpr (kStream) issue_next(); else issue(i + kDecStages - 1);
 
       float mx0 = kNegBig, mx1 = kNegBig;
 #pragma unroll
@@ -240,36 +287,57 @@ paged_decode_kernel(const DecodeParams p) {
         }
       }
       __syncwarp();  // all lanes are done with this stage before it is refilled
+      ++use_slot;
     }
-    cp_async_wait<0>();
+    if constexpr (!kStream) cp_async_wait<0>();
 
     l0 += __shfl_xor_sync(0xffffffffu, l0, 1);
     l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
     l1 += __shfl_xor_sync(0xffffffffu, l1, 1);
     l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
 
-    // ---- merge the four warps through shared memory (the ring is idle now) ----
-    __syncthreads();
-    float* sO = reinterpret_cast<float*>(smem);
-    float* sML = sO + kDecWarps * 16 * S::kMergeStride;
-    {
-      float* mine = sO + warp * 16 * S::kMergeStride;
+    // ---- merge the four warps through shared memory ----
+    if constexpr (kStream) {
+      // buffer of its own (rows of the group only): the rings keep receiving the next item's tiles meanwhile
+      constexpr int R = S::kStreamRows;
+      float* sO = reinterpret_cast<float*>(smem + S::kRingBytes);
+      float* sML = sO + kDecWarps * R * S::kMergeStride;
+      if (g < R) {
+        float* mine = sO + (warp * R + g) * S::kMergeStride;
 #pragma unroll
-      for (int j = 0; j < NT; ++j) {
-        *reinterpret_cast<float2*>(mine + g * S::kMergeStride + j * 8 + 2 * t) = make_float2(o[j][0], o[j][1]);
-        *reinterpret_cast<float2*>(mine + (g + 8) * S::kMergeStride + j * 8 + 2 * t) = make_float2(o[j][2], o[j][3]);
+        for (int j = 0; j < NT; ++j) *reinterpret_cast<float2*>(mine + j * 8 + 2 * t) = make_float2(o[j][0], o[j][1]);
+        if (t == 0) {
+          sML[(warp * R + g) * 2] = m0;
+          sML[(warp * R + g) * 2 + 1] = l0;
+        }
       }
-      if (t == 0) {
-        sML[(warp * 16 + g) * 2] = m0;
-        sML[(warp * 16 + g) * 2 + 1] = l0;
-        sML[(warp * 16 + g + 8) * 2] = m1;
-        sML[(warp * 16 + g + 8) * 2 + 1] = l1;
+      __syncthreads();
+      merge_and_write<T, D>(p, sO, sML, S::kMergeStride, rows_valid, h0, b, item, nsplit, R);
+      __syncthreads();  // the buffer is free for the next item
+    } else {
+      __syncthreads();  // the ring is idle now
+      float* sO = reinterpret_cast<float*>(smem);
+      float* sML = sO + kDecWarps * 16 * S::kMergeStride;
+      {
+        float* mine = sO + warp * 16 * S::kMergeStride;
+#pragma unroll
+        for (int j = 0; j < NT; ++j) {
+          *reinterpret_cast<float2*>(mine + g * S::kMergeStride + j * 8 + 2 * t) = make_float2(o[j][0], o[j][1]);
+          *reinterpret_cast<float2*>(mine + (g + 8) * S::kMergeStride + j * 8 + 2 * t) = make_float2(o[j][2], o[j][3]);
+        }
+        if (t == 0) {
+          sML[(warp * 16 + g) * 2] = m0;
+          sML[(warp * 16 + g) * 2 + 1] = l0;
+          sML[(warp * 16 + g + 8) * 2] = m1;
+          sML[(warp * 16 + g + 8) * 2 + 1] = l1;
+        }
       }
+      __syncthreads();
+      merge_and_write<T, D>(p, sO, sML, S::kMergeStride, rows_valid, h0, b, item, nsplit);
+      __syncthreads();  // the ring is handed back to the pipelines
     }
-    __syncthreads();
-    merge_and_write<T, D>(p, sO, sML, S::kMergeStride, rows_valid, h0, b, item, nsplit);
-    __syncthreads();  // the ring is handed back to the pipelines
   }
+  if constexpr (kStream) cp_async_wait<0>();   // only empty groups are left
 }
 
 // Reduces the partial results of sequences that were split, in item order.
@@ -312,20 +380,14 @@ static DecodeLayout decode_layout(int batch, int num_heads, int num_kv_heads, in
   return L;
 }
 
-template <typename T, int D>
-static int launch_decode(const DecodeParams& p, cudaStream_t st) {
-  using S = DecodeSmem<T, D>;
-  const size_t smem = S::kRingBytes + static_cast<size_t>(p.batch + 1) * sizeof(int);
-  // 227 KB per CTA is the sm_100 limit for static + dynamic shared memory together.
-  constexpr size_t kStaticSmem = 256;
-  if (smem + kStaticSmem > 227 * 1024)
-    return fail(MV_ERR_LIMIT, "paged_decode: batch %d needs %zu bytes of shared memory", p.batch, smem);
+template <typename T, int D, bool kStream>
+static int launch_decode_variant(const DecodeParams& p, size_t smem, cudaStream_t st) {
   static size_t attr_bytes[64] = {};  // per kernel instantiation and per device
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev < 0 || dev >= 64 || attr_bytes[dev] < smem) {
-    const cudaError_t e = cudaFuncSetAttribute(paged_decode_kernel<T, D>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                               static_cast<int>(smem));
+    const cudaError_t e = cudaFuncSetAttribute(paged_decode_kernel<T, D, kStream>,
+                                               cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
     if (e != cudaSuccess) {
       cudaGetLastError();
       return fail(MV_ERR_CUDA, "paged_decode: cudaFuncSetAttribute(%zu): %s", smem, cudaGetErrorString(e));
@@ -333,8 +395,25 @@ static int launch_decode(const DecodeParams& p, cudaStream_t st) {
     if (dev >= 0 && dev < 64) attr_bytes[dev] = smem;
   }
   const int grid = decode_grid(p);
-  paged_decode_kernel<T, D><<<grid, kDecThreads, smem, st>>>(p);
-  int rc = check_launch("paged_decode_kernel");
+  paged_decode_kernel<T, D, kStream><<<grid, kDecThreads, smem, st>>>(p);
+  return check_launch("paged_decode_kernel");
+}
+
+template <typename T, int D>
+static int launch_decode(const DecodeParams& p, cudaStream_t st) {
+  using S = DecodeSmem<T, D>;
+  const size_t plan = static_cast<size_t>(p.batch + 1) * sizeof(int);
+  const size_t smem = S::kRingBytes + plan;
+  // 227 KB per CTA is the sm_100 limit for static + dynamic shared memory together.
+  constexpr size_t kStaticSmem = 256;
+  if (smem + kStaticSmem > 227 * 1024)
+    return fail(MV_ERR_LIMIT, "paged_decode: batch %d needs %zu bytes of shared memory", p.batch, smem);
+  // the streaming variant when the group fits its merge buffer and two CTAs still fit an SM
+  const size_t smem_stream = smem + S::kStreamMergeBytes;
+  const bool stream = p.mtiles == 1 && p.group <= S::kStreamRows &&
+                      kDecCtasPerSM * (smem_stream + kStaticSmem + 1024) <= 227 * 1024;
+  int rc = stream ? launch_decode_variant<T, D, true>(p, smem_stream, st)
+                  : launch_decode_variant<T, D, false>(p, smem, st);
   if (rc) return rc;
   paged_decode_combine_kernel<T, D><<<dim3(p.batch, p.num_kv_heads), 128, 0, st>>>(p);
   return check_launch("paged_decode_combine_kernel");

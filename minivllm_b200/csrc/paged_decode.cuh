@@ -14,8 +14,8 @@ constexpr int kTileTok = 16;                    // tokens per warp tile
 constexpr int kCtaTok = kTileTok * kDecWarps;   // tokens per CTA step
 constexpr int kChunkMax = 2048;                 // longest KV chunk of one work item
 constexpr int kDecCtasPerSM = 2;
-constexpr int kDecWaves = 2;                    // work items aimed at per resident CTA (8 and 16 measured slower:
-                                                // every item refills its ring and merges its warps)
+constexpr int kDecWaves = 2;                    // work items aimed at per resident CTA; 4, 8 and 16 measured slower
+                                                // on most shapes (merge, partial results and combine pass per item)
 constexpr float kNegBig = -1e30f;               // finite "minus infinity" for running maxima
 
 struct DecodeParams {
@@ -140,20 +140,21 @@ __device__ __forceinline__ DecodeItem find_item(const DecodeParams& p, const int
 // After every warp wrote its unnormalised O rows (sO, row stride `stride`
 // floats) and its (m, l) pairs (sML) to shared memory: combine the warps and
 // write either the final output (sequence not split) or the partial result.
+// A warp's rows sit at (warp * rpw + row): rpw = 16 (the whole MMA tile) or fewer when only the first rows exist.
 template <typename T, int D>
 __device__ __forceinline__ void merge_and_write(const DecodeParams& p, const float* sO, const float* sML, int stride,
-                                                int rows_valid, int h0, int b, int item, int nsplit) {
+                                                int rows_valid, int h0, int b, int item, int nsplit, int rpw = 16) {
   for (int idx = threadIdx.x; idx < rows_valid * D; idx += kDecThreads) {
     const int row = idx / D, d = idx - row * D;
     float M = kNegBig;
 #pragma unroll
-    for (int ww = 0; ww < kDecWarps; ++ww) M = fmaxf(M, sML[(ww * 16 + row) * 2]);
+    for (int ww = 0; ww < kDecWarps; ++ww) M = fmaxf(M, sML[(ww * rpw + row) * 2]);
     float acc = 0.f, L = 0.f;
 #pragma unroll
     for (int ww = 0; ww < kDecWarps; ++ww) {
-      const float wgt = fast_exp2(sML[(ww * 16 + row) * 2] - M);
-      acc += wgt * sO[(ww * 16 + row) * stride + d];
-      L += wgt * sML[(ww * 16 + row) * 2 + 1];
+      const float wgt = fast_exp2(sML[(ww * rpw + row) * 2] - M);
+      acc += wgt * sO[(ww * rpw + row) * stride + d];
+      L += wgt * sML[(ww * rpw + row) * 2 + 1];
     }
     const int h = h0 + row;
     if (nsplit == 1) {
