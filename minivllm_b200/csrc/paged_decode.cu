@@ -5,13 +5,14 @@
 // Does the work of src/myvllm/layers/attention.py:283-473 of the reference
 // (one Triton program per (sequence, query head), scalar per-token loops, no
 // split, KV re-read per query head).  Design here:
-//   * work item = (sequence, KV chunk, KV head).  The chunk length is chosen
-//     on the device from sum(context_lens) so that the machine is filled
-//     whatever the batch looks like; the grid is persistent and depends on
+//   * the tokens of all sequences form one stream that is cut into segments of
+//     equal length; a work unit is (segment, KV head) and every resident CTA
+//     takes one, so each CTA streams the same number of bytes whatever the mix
+//     of context lengths ("stream-K" over the KV tokens).  The pieces of
+//     sequences inside a segment are the work items; a sequence that spans
+//     segments leaves partial results.  The segment length is chosen on the
+//     device from sum(context_lens); the grid is persistent and depends on
 //     shapes only (graph-capturable).  Every CTA recomputes the same plan.
-//     The chunk length only fixes how many items a sequence gets; its tokens
-//     are then spread evenly over them (items of similar length: CTAs take
-//     items in a fixed stride).
 //   * a CTA is 4 independent warps.  Each warp streams its own 16-token tiles
 //     of K and V through a private cp.async ring in shared memory (XOR-swizzled
 //     16-byte chunks, conflict-free for ldmatrix), so the main loop has no
@@ -66,15 +67,14 @@ paged_decode_kernel(const DecodeParams p) {
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int g = lane >> 2, t = lane & 3;
 
-  const int chunk = build_plan(p, s_start, s_red);
-  const int total_items = s_start[p.batch];
+  const DecodePlan plan = build_plan(p, s_start, s_red);
   if (blockIdx.x == 0) {
-    for (int b = tid; b < p.batch; b += kDecThreads)
-      p.binfo[b] = make_int2(s_start[b], s_start[b + 1] - s_start[b]);
+    for (int b = tid; b < p.batch; b += kDecThreads) p.binfo[b] = seq_items(s_start, plan, b);
   }
+  zero_empty_sequences<T, D>(p, s_start);
 
   const int ydim = p.num_kv_heads * p.mtiles;
-  const long long total_work = static_cast<long long>(total_items) * ydim;
+  const long long n_units = static_cast<long long>(plan.n_seg) * ydim;
   const uint32_t ring = smem_u32(smem) + warp * S::kWarpBytes;
   const T* kc = static_cast<const T*>(p.k_cache);
   const T* vc = static_cast<const T*>(p.v_cache);
@@ -85,13 +85,12 @@ paged_decode_kernel(const DecodeParams p) {
     int b, nsplit, tok_begin, tok_end, kvh, mt, item, my_tiles;
     const int32_t* table;
   };
-  auto load_item = [&](long long w, Item& it) -> bool {
-    if (w >= total_work) return false;
-    it.item = static_cast<int>(w / ydim);
-    const int y = static_cast<int>(w - static_cast<long long>(it.item) * ydim);
-    it.kvh = y / p.mtiles;
-    it.mt = y - it.kvh * p.mtiles;
-    const DecodeItem di = find_item(p, s_start, it.item, chunk);
+  auto load_item = [&](const ItemWalk& at, Item& it) -> bool {
+    if (at.b < 0) return false;
+    it.kvh = at.y / p.mtiles;
+    it.mt = at.y - it.kvh * p.mtiles;
+    const DecodeItem di = piece_of(s_start, plan, at.b, at.seg);
+    it.item = di.item;
     it.b = di.b; it.nsplit = di.nsplit; it.tok_begin = di.tok_begin; it.tok_end = di.tok_end;
     it.table = p.block_tables + static_cast<int64_t>(di.b) * p.bt_stride;
     // tiles of this warp: tokens tok_begin + (i*kDecWarps + warp)*16
@@ -131,14 +130,14 @@ paged_decode_kernel(const DecodeParams p) {
   // kStream: the load side walks the warp's tile stream on its own, two ring slots ahead of the MMAs.  Every
   // slot is one cp.async group (empty once the stream has ended), so "at most one group pending" always
   // means that the slot about to be consumed has landed.
-  long long load_w = blockIdx.x;
+  ItemWalk load_at;
   Item load_it;
   bool load_valid = false;
   int load_tile = 0, load_slot = 0, use_slot = 0;
   auto issue_next = [&]() {
     while (load_valid && load_tile >= load_it.my_tiles) {
-      load_w += gridDim.x;
-      load_valid = load_item(load_w, load_it);
+      walk_next(p, s_start, plan, ydim, n_units, gridDim.x, load_at);
+      load_valid = load_item(load_at, load_it);
       load_tile = 0;
     }
     if (load_valid) {
@@ -149,14 +148,17 @@ paged_decode_kernel(const DecodeParams p) {
     ++load_slot;
   };
   if constexpr (kStream) {
-    load_valid = load_item(load_w, load_it);
+    walk_start(p, s_start, plan, ydim, n_units, blockIdx.x, load_at);
+    load_valid = load_item(load_at, load_it);
 #pragma unroll
     for (int i = 0; i < kDecStages - 1; ++i) issue_next();
   }
 
-  for (long long w = blockIdx.x; w < total_work; w += gridDim.x) {
+  ItemWalk at;
+  for (walk_start(p, s_start, plan, ydim, n_units, blockIdx.x, at); at.b >= 0;
+       walk_next(p, s_start, plan, ydim, n_units, gridDim.x, at)) {
     Item cur;
-    load_item(w, cur);
+    load_item(at, cur);
     const int item = cur.item, kvh = cur.kvh, mt = cur.mt, b = cur.b, nsplit = cur.nsplit, my_tiles = cur.my_tiles;
     const int rows_valid = min(16, p.group - mt * 16);
     const int h0 = kvh * p.group + mt * 16;
@@ -453,6 +455,8 @@ extern "C" int mv_paged_decode(void* out, const void* q, const void* k_cache, co
     return fail(MV_ERR_ALIGN, "paged_decode: pointers must be 16-byte aligned");
   if (bt_stride < max_blocks) return fail(MV_ERR_SHAPE, "paged_decode: block table stride smaller than its width");
   if (num_blocks * block_size > 0x7fffffffLL) return fail(MV_ERR_LIMIT, "paged_decode: more than 2^31 cache slots");
+  if (static_cast<int64_t>(batch) * max_blocks * block_size > 0x7fffffffLL)
+    return fail(MV_ERR_LIMIT, "paged_decode: batch * max_blocks * block_size exceeds 2^31 tokens");
   const DecodeLayout L = decode_layout(batch, num_heads, num_kv_heads, head_dim, max_blocks, block_size);
   if (workspace_bytes < L.total)
     return fail(MV_ERR_WORKSPACE, "paged_decode: workspace %lld < %lld bytes", (long long)workspace_bytes, (long long)L.total);

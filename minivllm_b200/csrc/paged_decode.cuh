@@ -12,10 +12,10 @@ constexpr int kDecThreads = kDecWarps * 32;
 constexpr int kDecStages = 3;
 constexpr int kTileTok = 16;                    // tokens per warp tile
 constexpr int kCtaTok = kTileTok * kDecWarps;   // tokens per CTA step
-constexpr int kChunkMax = 2048;                 // longest KV chunk of one work item
+constexpr int kChunkMax = 2048;                 // only sizes the scratch bound below (an older plan cut sequences at this length)
 constexpr int kDecCtasPerSM = 2;
-constexpr int kDecWaves = 2;                    // work items aimed at per resident CTA; 4, 8 and 16 measured slower
-                                                // on most shapes (merge, partial results and combine pass per item)
+constexpr int kDecWaves = 1;                    // work units per resident CTA: units are equal in length, so one each
+                                                // is balanced; 2 and 4 measured slower (more pieces to merge)
 constexpr float kNegBig = -1e30f;               // finite "minus infinity" for running maxima
 
 struct DecodeParams {
@@ -40,8 +40,8 @@ struct DecodeParams {
   float* part_o;    // (item, head, D)
 };
 
-// Work items aimed at per (KV head, row tile): enough to give every resident
-// CTA kDecWaves items.  Shapes only, so host and device agree.
+// Segments of the token stream per (KV head, row tile): every resident CTA gets
+// kDecWaves units.  Shapes only, so host and device agree.
 __host__ __device__ inline int decode_target_items(int num_kv_heads, int mtiles) {
   const int t = (kNumSMs * kDecCtasPerSM * kDecWaves) / (num_kv_heads * mtiles);
   return t < 1 ? 1 : t;
@@ -62,35 +62,24 @@ __device__ __forceinline__ int load_ctx(const DecodeParams& p, int b) {
   return static_cast<int>(c);
 }
 
-// Every CTA builds the same plan: chunk length and s_start[b] = first item of
-// sequence b (s_start[batch] = number of items).  Returns the chunk length.
-__device__ inline int build_plan(const DecodeParams& p, int* s_start, long long* s_red) {
+// ---- the work plan --------------------------------------------------------------------------------
+// The tokens of all sequences form one stream (sequence after sequence).  It is cut into `n_seg`
+// segments of equal length `seg_len`; a work UNIT is (segment, KV head, row tile) and a CTA takes whole
+// units, so every CTA streams the same number of tokens whatever the mix of context lengths.  Inside a
+// unit the work ITEMS are the pieces of sequences that the segment covers: item id = sequence index +
+// segment index, which is unique, increases along the stream, and is contiguous per sequence (a sequence
+// that spans segments s0..s1 owns ids b+s0 .. b+s1: its partial results, merged by the combine kernel).
+// Every CTA builds the same plan: s_tok[b] = tokens before sequence b, s_tok[batch] = all tokens.
+struct DecodePlan {
+  int seg_len, n_seg;
+};
+__device__ inline DecodePlan build_plan(const DecodeParams& p, int* s_tok, long long* s_red) {
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  long long sum = 0;
-  for (int b = tid; b < p.batch; b += kDecThreads) sum += load_ctx(p, b);
-#pragma unroll
-  for (int off = 16; off > 0; off >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, off);
-  if (lane == 0) s_red[warp] = sum;
-  __syncthreads();
-  long long total = 0;
-#pragma unroll
-  for (int w = 0; w < kDecWarps; ++w) total += s_red[w];
-  long long chunk = (total + p.target_items - 1) / p.target_items;
-  chunk = ((chunk + kCtaTok - 1) / kCtaTok) * kCtaTok;
-  if (chunk < kCtaTok) chunk = kCtaTok;
-  if (chunk > kChunkMax) chunk = kChunkMax;
-  const int ch = static_cast<int>(chunk);
-  __syncthreads();  // s_red is reused below
-
   int carry = 0;
-  if (tid == 0) s_start[0] = 0;
+  if (tid == 0) s_tok[0] = 0;
   for (int base = 0; base < p.batch; base += kDecThreads) {
     const int b = base + tid;
-    int n = 0;
-    if (b < p.batch) {
-      n = (load_ctx(p, b) + ch - 1) / ch;
-      if (n < 1) n = 1;  // an empty sequence still owns one item, which writes zeros
-    }
+    const int n = b < p.batch ? load_ctx(p, b) : 0;
     int incl = n;
 #pragma unroll
     for (int off = 1; off < 32; off <<= 1) {
@@ -106,35 +95,90 @@ __device__ inline int build_plan(const DecodeParams& p, int* s_start, long long*
       if (w < warp) wofs += v;
       tot += v;
     }
-    if (b < p.batch) s_start[b + 1] = carry + wofs + incl;
+    if (b < p.batch) s_tok[b + 1] = carry + wofs + incl;
     carry += tot;
     __syncthreads();
   }
-  return ch;
+  const int total = carry;
+  DecodePlan plan;
+  int seg = (total + p.target_items - 1) / p.target_items;
+  seg = ((seg + kCtaTok - 1) / kCtaTok) * kCtaTok;
+  if (seg < kCtaTok) seg = kCtaTok;
+  plan.seg_len = seg;
+  plan.n_seg = (total + seg - 1) / seg;   // <= target_items
+  return plan;
 }
 
+// (first item id, number of items) of sequence b; an empty sequence has none.
+__device__ __forceinline__ int2 seq_items(const int* s_tok, const DecodePlan& plan, int b) {
+  const int t0 = s_tok[b], t1 = s_tok[b + 1];
+  if (t1 <= t0) return make_int2(0, 0);
+  const int s0 = t0 / plan.seg_len, s1 = (t1 - 1) / plan.seg_len;
+  return make_int2(b + s0, s1 - s0 + 1);
+}
 
-// Which (sequence, chunk) a work item is, from the plan in shared memory.
-struct DecodeItem {
-  int b, nsplit, tok_begin, tok_end;
-};
-__device__ __forceinline__ DecodeItem find_item(const DecodeParams& p, const int* s_start, int item, int chunk) {
+// The sequence whose tokens include stream position `pos` (pos < total): the last b with s_tok[b] <= pos
+// (empty sequences share their successor's prefix and are skipped by "last").
+__device__ __forceinline__ int seq_at(const DecodeParams& p, const int* s_tok, int pos) {
   int lo = 0, hi = p.batch - 1;
-  while (lo < hi) {  // last b with s_start[b] <= item
+  while (lo < hi) {
     const int mid = (lo + hi + 1) >> 1;
-    if (s_start[mid] <= item) lo = mid; else hi = mid - 1;
+    if (s_tok[mid] <= pos) lo = mid; else hi = mid - 1;
   }
+  return lo;
+}
+
+// One piece of a sequence inside a segment.
+struct DecodeItem {
+  int b, nsplit, tok_begin, tok_end, item;
+};
+__device__ __forceinline__ DecodeItem piece_of(const int* s_tok, const DecodePlan& plan, int b, int seg) {
+  const int t0 = s_tok[b], t1 = s_tok[b + 1];
+  const int g0 = seg * plan.seg_len, g1 = g0 + plan.seg_len;
   DecodeItem it;
-  it.b = lo;
-  it.nsplit = s_start[lo + 1] - s_start[lo];
-  // The sequence's tokens are spread evenly over its items (in whole CTA steps) instead of full chunks plus a
-  // short remainder: CTAs take items in a fixed stride, so items of similar length mean a similar load.
-  const int ctx = load_ctx(p, lo);
-  int per = (ctx + it.nsplit - 1) / it.nsplit;
-  per = ((per + kCtaTok - 1) / kCtaTok) * kCtaTok;   // <= chunk, which is a multiple of kCtaTok
-  it.tok_begin = (item - s_start[lo]) * per;
-  it.tok_end = min(ctx, it.tok_begin + per);
+  it.b = b;
+  it.item = b + seg;
+  it.tok_begin = max(g0 - t0, 0);
+  it.tok_end = min(g1, t1) - t0;
+  it.nsplit = (t1 - 1) / plan.seg_len - t0 / plan.seg_len + 1;
   return it;
+}
+
+// Walks the items of the units u = first, first + stride, ... in order.
+struct ItemWalk {
+  long long unit;
+  int seg, y, b;      // b < 0: finished
+};
+__device__ __forceinline__ void walk_enter_unit(const DecodeParams& p, const int* s_tok, const DecodePlan& plan,
+                                                int ydim, long long n_units, ItemWalk& w) {
+  if (w.unit >= n_units) { w.b = -1; return; }
+  w.seg = static_cast<int>(w.unit / ydim);
+  w.y = static_cast<int>(w.unit - static_cast<long long>(w.seg) * ydim);
+  w.b = seq_at(p, s_tok, w.seg * plan.seg_len);
+}
+__device__ __forceinline__ void walk_start(const DecodeParams& p, const int* s_tok, const DecodePlan& plan, int ydim,
+                                           long long n_units, long long first, ItemWalk& w) {
+  w.unit = first;
+  walk_enter_unit(p, s_tok, plan, ydim, n_units, w);
+}
+__device__ __forceinline__ void walk_next(const DecodeParams& p, const int* s_tok, const DecodePlan& plan, int ydim,
+                                          long long n_units, long long stride, ItemWalk& w) {
+  const int seg_end = (w.seg + 1) * plan.seg_len;
+  int b = w.b + 1;
+  while (b < p.batch && s_tok[b + 1] == s_tok[b]) ++b;   // empty sequences own no tokens
+  if (b < p.batch && s_tok[b] < seg_end) { w.b = b; return; }
+  w.unit += stride;
+  walk_enter_unit(p, s_tok, plan, ydim, n_units, w);
+}
+
+// Rows of sequences without any token: nobody's item covers them, the CTAs share out writing their zeros.
+template <typename T, int D>
+__device__ __forceinline__ void zero_empty_sequences(const DecodeParams& p, const int* s_tok) {
+  for (int b = blockIdx.x; b < p.batch; b += gridDim.x) {
+    if (s_tok[b + 1] != s_tok[b]) continue;
+    T* row = static_cast<T*>(p.out) + static_cast<int64_t>(b) * p.num_heads * D;
+    for (int i = threadIdx.x; i < p.num_heads * D; i += kDecThreads) row[i] = Elem<T>::from_f(0.f);
+  }
 }
 
 // After every warp wrote its unnormalised O rows (sO, row stride `stride`

@@ -77,26 +77,25 @@ paged_decode_int8_kernel(const DecodeParams p) {
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int g = lane >> 2, t = lane & 3;
 
-  const int chunk = build_plan(p, s_start, s_red);
-  const int total_items = s_start[p.batch];
+  const DecodePlan plan = build_plan(p, s_start, s_red);
   if (blockIdx.x == 0) {
-    for (int b = tid; b < p.batch; b += kDecThreads)
-      p.binfo[b] = make_int2(s_start[b], s_start[b + 1] - s_start[b]);
+    for (int b = tid; b < p.batch; b += kDecThreads) p.binfo[b] = seq_items(s_start, plan, b);
   }
+  zero_empty_sequences<T, D>(p, s_start);
 
   const int ydim = p.num_kv_heads * p.mtiles;
-  const long long total_work = static_cast<long long>(total_items) * ydim;
+  const long long n_units = static_cast<long long>(plan.n_seg) * ydim;
   const uint32_t ring = smem_u32(smem) + warp * S::kWarpBytes;
   const int8_t* kc = static_cast<const int8_t*>(p.k_cache);
   const int8_t* vc = static_cast<const int8_t*>(p.v_cache);
   const int bs = p.block_size;
 
-  for (long long w = blockIdx.x; w < total_work; w += gridDim.x) {
-    const int item = static_cast<int>(w / ydim);
-    const int y = static_cast<int>(w - static_cast<long long>(item) * ydim);
-    const int kvh = y / p.mtiles, mt = y - kvh * p.mtiles;
-    const DecodeItem di = find_item(p, s_start, item, chunk);
-    const int b = di.b, nsplit = di.nsplit, tok_begin = di.tok_begin, tok_end = di.tok_end;
+  ItemWalk at;
+  for (walk_start(p, s_start, plan, ydim, n_units, blockIdx.x, at); at.b >= 0;
+       walk_next(p, s_start, plan, ydim, n_units, gridDim.x, at)) {
+    const int kvh = at.y / p.mtiles, mt = at.y - kvh * p.mtiles;
+    const DecodeItem di = piece_of(s_start, plan, at.b, at.seg);
+    const int item = di.item, b = di.b, nsplit = di.nsplit, tok_begin = di.tok_begin, tok_end = di.tok_end;
     const int32_t* table = p.block_tables + static_cast<int64_t>(b) * p.bt_stride;
     const int rows_valid = min(16, p.group - mt * 16);
     const int h0 = kvh * p.group + mt * 16;

@@ -1,6 +1,7 @@
 """Engine-level parity on the GPU: the same harness model, scheduler and runner,
 with the CUDA attention path (eager and CUDA-graph decode) against the CPU-oracle
-attention operators.  Greedy token streams must be identical for the first 32 tokens."""
+attention operators.  Greedy token streams must be identical for the first 32 tokens, up to near-ties of the
+logits (see _assert_same_up_to_near_ties)."""
 import pytest
 import torch
 
@@ -33,6 +34,40 @@ def _run(enforce_eager, oracle=False, max_tokens=40, config=None):
     return out["token_ids"], eng
 
 
+def _assert_same_up_to_near_ties(ours, ref, what):
+    """Greedy streams must agree token for token, except that a stream may leave the other one where the two
+    candidate tokens are a near-tie: kernels that differ only in summation order (how the KV tokens of a batch
+    are cut into work items depends on the batch) can order two almost equal bf16 logits differently.  At the
+    first divergence of a request the logits are recomputed by a full forward pass over the common history
+    with the CPU-oracle attention, and the two tokens must be within 3 bf16 rounding steps of each other and
+    of the maximum.  Nothing after a legitimate divergence is compared: the histories differ from there on."""
+    from minivllm_b200.utils.context import reset_context, set_context
+    prompts = _prompts()
+    model = None
+    for r, (x, y) in enumerate(zip(ours, ref)):
+        assert len(x) == len(y)
+        i = next((k for k, (a, b) in enumerate(zip(x, y)) if a != b), None)
+        if i is None:
+            continue
+        if model is None:
+            eng = LLMEngine(dict(CONFIG, enforce_eager=True))
+            model = swap_in_oracle_attention(eng.model_runner.model)
+        ids = torch.tensor(prompts[r] + y[:i], dtype=torch.int64, device="cuda")
+        n = ids.numel()
+        cu = torch.tensor([0, n], dtype=torch.int32, device="cuda")
+        set_context(True, cu, cu, n, n, None, None, None, positions=torch.arange(n, device="cuda"),
+                    last_token_index=torch.tensor([n - 1], device="cuda"))
+        with torch.inference_mode():
+            logits = model.compute_logits(model(ids)).float()[0]
+        reset_context()
+        top = float(logits.max())
+        la, lb = float(logits[x[i]]), float(logits[y[i]])
+        step = 2.0 ** -8 * max(abs(top), 1e-6)
+        assert abs(la - lb) <= 3 * step and top - min(la, lb) <= 3 * step, \
+            f"{what}: request {r} diverges at token {i} ({x[i]} vs {y[i]}) and it is no near-tie: " \
+            f"logits {la} / {lb}, maximum {top}"
+
+
 def test_graph_decode_equals_eager_decode():
     eager, _ = _run(True)
     graph, eng = _run(False)
@@ -44,8 +79,7 @@ def test_graph_decode_equals_eager_decode():
 def test_greedy_stream_matches_oracle_attention_for_32_tokens():
     ours, _ = _run(False, max_tokens=32)
     ref, _ = _run(True, oracle=True, max_tokens=32)
-    first_diff = [next((i for i, (a, b) in enumerate(zip(x, y)) if a != b), None) for x, y in zip(ours, ref)]
-    assert ours == ref, f"first divergence per request: {first_diff}"
+    _assert_same_up_to_near_ties(ours, ref, "CUDA attention against the oracle attention")
 
 
 def test_continuous_batching_with_preemption_keeps_streams():
@@ -54,7 +88,7 @@ def test_continuous_batching_with_preemption_keeps_streams():
     big, _ = _run(False, max_tokens=24)
     small_cfg = dict(CONFIG, num_kv_blocks=9)       # 6 requests x up to 4 blocks do not fit
     small, eng = _run(False, max_tokens=24, config=small_cfg)
-    assert small == big
+    _assert_same_up_to_near_ties(small, big, "with preemption against without")
 
 
 def test_temperature_sampling_runs_in_graph_mode():

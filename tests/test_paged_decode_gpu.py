@@ -103,6 +103,26 @@ def test_decode_negative_table_entries_and_empty_rows():
     assert torch.count_nonzero(got[3]) == 0 and not torch.isnan(got).any()
 
 
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+def test_decode_segment_cuts_on_and_off_sequence_boundaries(dtype):
+    """The kernel cuts the concatenated tokens of the batch into equal segments.  37 sequences of 128 tokens with
+    8 KV heads put every cut exactly on a sequence boundary; then some sequences are emptied (they own no token,
+    their rows are zeros) and one is shortened, which moves every cut into the middle of a sequence."""
+    d = synth.decode_inputs(seed=46, batch=37, ctx_lo=128, ctx_hi=128, num_heads=16, num_kv_heads=8, head_dim=128,
+                            block_size=64)
+    got, want = _gpu_decode(d, dtype), _oracle_decode(d, dtype)
+    assert float((got - want).abs().max()) < TOL + (2.0 ** -8 if dtype == torch.bfloat16 else 0) * float(want.abs().max())
+    cl = d["context_lens"].clone()
+    cl[0] = 0
+    cl[5:9] = 0
+    cl[36] = 0
+    cl[20] = 77
+    got, want = _gpu_decode(d, dtype, context_lens=cl), _oracle_decode(d, dtype, context_lens=cl)
+    assert float((got - want).abs().max()) < TOL + (2.0 ** -8 if dtype == torch.bfloat16 else 0) * float(want.abs().max())
+    for b in (0, 5, 8, 36):
+        assert torch.count_nonzero(got[b]) == 0
+
+
 def test_decode_long_context_is_split():
     """One sequence far longer than a chunk: exercises the partial-result path and the combine kernel."""
     d = synth.decode_inputs(seed=45, batch=2, ctx_lo=9000, ctx_hi=12000, num_heads=8, num_kv_heads=2, head_dim=128,
