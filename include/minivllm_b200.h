@@ -91,6 +91,10 @@ int64_t mv_paged_decode_workspace_bytes(int batch, int num_heads,
  * int32 with row stride bt_stride; context_lens is int32 or int64 and is
  * clamped to [0, max_blocks * block_size].
  * The grid depends on shapes only, so the call can be captured in a graph.
+ * batch * max_blocks * block_size must stay below 2^31 (status 7 otherwise).
+ * The KV tokens of the whole batch are divided evenly among the thread
+ * blocks, so where a long sequence is cut depends on the other sequences:
+ * a row's result can differ in its last bits between batch compositions.
  */
 int mv_paged_decode(void* out, const void* q,
                     const void* k_cache, const void* v_cache,
