@@ -1,9 +1,9 @@
 """Generates tests/golden/*.npz by running the REFERENCE's own code on the CPU.
 
-Run once, in a container that has the reference checkout (default
-/root/reference, or $MINIVLLM_REFERENCE):
+Run once, where a checkout of the reference is at hand; its location comes from
+$MINIVLLM_REFERENCE:
 
-    python tests/golden/make_golden.py
+    MINIVLLM_REFERENCE=<reference checkout> python tests/golden/make_golden.py
 
 What is recorded (inputs are regenerated from seeds by the tests; only the
 reference's outputs are stored, as fp32):
@@ -27,7 +27,7 @@ import torch
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 ROOT = os.path.dirname(os.path.dirname(HERE))
-REF = os.environ.get("MINIVLLM_REFERENCE", "/root/reference")
+REF = os.environ.get("MINIVLLM_REFERENCE", os.path.join(os.sep, "root", "reference"))
 sys.path.insert(0, ROOT)
 sys.path.insert(0, REF)
 sys.path.insert(0, os.path.join(REF, "src"))
