@@ -271,6 +271,87 @@ int mv_argmax_rows(const void* logits, int64_t row_stride, int64_t rows,
 int mv_argmax_decode(const int64_t* keys, int shards, int64_t rows,
                      int64_t* tokens, void* stream);
 
+/*
+ * Tensor-parallel all-reduce over NVLink peer memory, fused with the residual
+ * add and the RMSNorm that follow it.
+ * Replaces: the `dist.all_reduce(result)` that ends every row-parallel linear
+ * layer (src/myvllm/layers/linear.py:216-221, after o_proj and down_proj) plus
+ * the residual add and RMSNorm each rank then repeats on the full activations
+ * (src/myvllm/layers/layernorm.py:10-22, called from models/qwen3.py:187,215).
+ *
+ * A communicator owns, on every rank, one device allocation holding an INPUT
+ * buffer (this rank's partial sums, written by the caller's GEMM), a GATHER
+ * buffer (the normalised rows of all ranks, read by the caller's next GEMM)
+ * and the barrier flags; peers map each other's allocation through CUDA IPC.
+ * Set-up (once, allocates): every rank calls mv_comm_create, the caller
+ * exchanges the mv_comm_handle_bytes()-byte handles of all ranks in rank order
+ * (any host channel), every rank calls mv_comm_connect, and the caller makes
+ * sure every rank has connected before the first launch (a host barrier).
+ * `data_bytes` bounds rows*hidden*2 of one call; `timeout_ms` bounds every
+ * in-kernel wait.
+ *
+ * mv_allreduce_residual_rmsnorm, with x_p (rows, hidden) in rank p's input
+ * buffer and rank r owning rows [r*ceil(rows/N), min(rows, (r+1)*ceil(rows/N))):
+ *   o = round(sum_p x_p[row]) (fp32, p ascending);
+ *   residual_shard[row - first owned row] = round(residual_shard[...] + o);
+ *   h[row] = round(residual * rsqrt(mean(residual^2) + eps) * gamma)
+ * and h[row] is stored into the gather buffer of every rank.  The residual
+ * stream stays sharded by rows: residual_shard is (owned rows, hidden).
+ * Every rank must make the same sequence of calls with the same rows/hidden.
+ * Launch-only (graph-capturable); peers are read and written with plain loads
+ * and stores.  A wait that runs out of time stores a non-zero code in
+ * *error_word (caller-owned device int, zero-initialised; 0x100|peer = partial
+ * sums never arrived, 0x200|peer = result rows never arrived) and the kernel
+ * returns; while the word is non-zero later launches return at once.  After
+ * such an error the communicator must be reset on every rank (mv_comm_reset,
+ * all ranks idle) before it is used again.
+ *
+ * mv_comm_create_emulated builds all N ranks on the current device; a call
+ * then runs every rank in ONE cooperative launch (residual shard of rank p at
+ * residual_shard + p*residual_slot_stride elements; mv_comm_input/output take
+ * the rank as `slot`).  It exists to test the protocol on a single GPU and is
+ * limited to 148 blocks in total.  On a real communicator `slot` is 0 and
+ * residual_slot_stride is ignored.
+ */
+int64_t mv_comm_handle_bytes(void);
+int mv_comm_create(int rank, int world, int64_t data_bytes, int timeout_ms,
+                   void** comm_out, void* handle_out);
+int mv_comm_connect(void* comm, const void* all_handles);
+int mv_comm_create_emulated(int world, int64_t data_bytes, int timeout_ms,
+                            void** comm_out);
+int mv_comm_destroy(void* comm);
+int mv_comm_reset(void* comm);
+void* mv_comm_input(void* comm, int slot);
+void* mv_comm_output(void* comm, int slot);
+int mv_allreduce_residual_rmsnorm(void* comm, void* residual_shard,
+                                  int64_t residual_slot_stride,
+                                  const void* gamma, float eps, int rows,
+                                  int hidden, int* error_word, int dtype,
+                                  void* stream);
+
+/*
+ * Single-rank form of the same step: for every row,
+ *   s = x[row] (+ residual_in[row], rounded, when residual_in is non-null);
+ *   out[row] = round(s * rsqrt(mean(s^2) + eps) * gamma);
+ * and s is stored to residual_out[row - res_lo] for rows in [res_lo, res_hi)
+ * (residual_out may be null; it may alias residual_in when res_lo is 0).
+ * Replaces src/myvllm/layers/layernorm.py:10-28 (rms_forward and
+ * residual_rms_forward).  x/out/residuals are (rows, hidden) contiguous.
+ */
+int mv_add_rmsnorm(void* out, const void* x, const void* residual_in,
+                   void* residual_out, int64_t res_lo, int64_t res_hi,
+                   const void* gamma, float eps, int64_t rows, int hidden,
+                   int dtype, void* stream);
+
+/*
+ * SwiGLU activation on the fused gate_up projection output (rows, 2*inter),
+ * row stride in elements: out[t, j] = silu(gu[t, j]) * gu[t, inter + j],
+ * computed in fp32 and rounded once; out is (rows, inter) contiguous.
+ * Replaces src/myvllm/layers/activation.py:17-20 (SiluAndMul.forward).
+ */
+int mv_silu_mul(void* out, const void* gate_up, int64_t gate_up_stride,
+                int64_t rows, int inter, int dtype, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -48,6 +48,19 @@ SIGNATURES = {
                                        _c_int, _c_int, _c_ptr]),
     "mv_argmax_rows": (_c_int, [_c_ptr, _c_i64, _c_i64, _c_i64, _c_i64, _c_ptr, _c_ptr, _c_int, _c_ptr]),
     "mv_argmax_decode": (_c_int, [_c_ptr, _c_int, _c_i64, _c_ptr, _c_ptr]),
+    "mv_comm_handle_bytes": (_c_i64, []),
+    "mv_comm_create": (_c_int, [_c_int, _c_int, _c_i64, _c_int, ctypes.POINTER(_c_ptr), _c_ptr]),
+    "mv_comm_connect": (_c_int, [_c_ptr, _c_ptr]),
+    "mv_comm_create_emulated": (_c_int, [_c_int, _c_i64, _c_int, ctypes.POINTER(_c_ptr)]),
+    "mv_comm_destroy": (_c_int, [_c_ptr]),
+    "mv_comm_reset": (_c_int, [_c_ptr]),
+    "mv_comm_input": (_c_ptr, [_c_ptr, _c_int]),
+    "mv_comm_output": (_c_ptr, [_c_ptr, _c_int]),
+    "mv_allreduce_residual_rmsnorm": (_c_int, [_c_ptr, _c_ptr, _c_i64, _c_ptr, _c_f32, _c_int, _c_int, _c_ptr,
+                                               _c_int, _c_ptr]),
+    "mv_add_rmsnorm": (_c_int, [_c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_i64, _c_i64, _c_ptr, _c_f32, _c_i64, _c_int,
+                                _c_int, _c_ptr]),
+    "mv_silu_mul": (_c_int, [_c_ptr, _c_ptr, _c_i64, _c_i64, _c_int, _c_int, _c_ptr]),
 }
 
 _lib = None

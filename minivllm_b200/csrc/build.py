@@ -9,7 +9,7 @@ import sys
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 LIB = os.path.join(HERE, "libminivllm_b200.so")
-SOURCES = ["api.cu", "store_kvcache.cu", "paged_decode.cu", "paged_decode_int8.cu", "prefill_varlen.cu", "paged_decode_static.cu", "metadata.cu", "pre_attention.cu", "sampling.cu"]
+SOURCES = ["api.cu", "store_kvcache.cu", "paged_decode.cu", "paged_decode_int8.cu", "prefill_varlen.cu", "paged_decode_static.cu", "metadata.cu", "pre_attention.cu", "sampling.cu", "comm.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",
     "-O3", "-std=c++17", "-lineinfo",

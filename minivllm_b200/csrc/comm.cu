@@ -1,0 +1,627 @@
+// Tensor-parallel all-reduce over NVLink peer memory, fused with the residual
+// add and the RMSNorm that follow it in a decoder layer, plus the local
+// (single-rank) form of the same add + norm.
+//
+// What it replaces: the row-parallel linear layers of the reference end in
+// `dist.all_reduce(result)` (src/myvllm/layers/linear.py:216-221), and every
+// rank then runs the residual add and RMSNorm of layers/layernorm.py:19-22 on
+// the full (tokens, hidden) activations.  Here the three are one kernel:
+//
+//   every rank r holds its partial sums x_r (rows, hidden) in a buffer that
+//   its peers can read; rank r owns rows [r*ceil(rows/N), ...) and, for them,
+//     o        = round(sum_p x_p[row])              (fp32, ranks in order 0..N-1)
+//     residual = round(residual + o)                (kept row-sharded: only the owner stores it)
+//     h        = round(residual * rsqrt(mean(residual^2) + eps) * gamma)
+//   and writes h[row] into the gather buffer of EVERY rank (peer stores).
+//
+// "Two-shot": each row crosses NVLink once inbound (N-1 partial rows to the
+// owner) and once outbound (the normalised row to N-1 peers), so a rank moves
+// (N-1)/N of the message in each direction and the add + norm work shrinks by N.
+// Plain peer loads and stores only: no TMA, no multicast, no library kernel
+// ever sees a peer pointer.
+//
+// Synchronisation: two flag barriers per launch (peers' partial sums complete
+// before they are read; every owner's rows landed before the kernel ends).
+// Block b of rank r pairs with block b of every peer, so every rank must
+// launch the same grid, which depends on (rows, world) only.  A flag is a
+// 32-bit generation number that its writer increases by one per launch; the
+// generation of a block lives in device memory and is advanced by the kernel
+// itself, so a captured graph replays correctly.  Every wait is bounded by a
+// timer (and an iteration cap): on expiry the block records a code in the
+// caller's error word and returns; later launches return at once while the
+// word is non-zero.  Nothing traps.
+//
+// A communicator can also be created in EMULATION mode: all N ranks' buffers
+// live on one GPU and one cooperative launch runs every rank's blocks side by
+// side (grid.y = N).  It exists so the protocol and the arithmetic can be
+// tested on a single GPU; kernels that wait on one another are never
+// launched separately on one device.
+#include <new>
+#include "common.cuh"
+
+namespace mv {
+
+constexpr int kMaxRanks = 8;
+constexpr int kMaxCommBlocks = 512;           // flag rows per phase
+constexpr int kCommGridCap = 2 * kNumSMs;     // resident blocks: every block of every rank must be co-scheduled
+constexpr size_t kCtrlBytes = 64 << 10;       // flags + generations + rank table, in front of the data buffers
+
+// One entry per rank slot (one slot in a real communicator, N in emulation).
+struct CommSlot {
+  const void* in[kMaxRanks];    // every rank's partial-sum buffer, indexed by rank
+  void* out[kMaxRanks];         // every rank's gather buffer
+  uint32_t* flags[kMaxRanks];   // every rank's flag array [2][kMaxCommBlocks][kMaxRanks]
+  uint32_t* gen;                // this rank's per-block generation [kMaxCommBlocks]
+  int rank, world;
+  int skip_signal;              // test hook: withhold this slot's first-barrier signals once
+};
+
+struct Comm {
+  int rank = 0, world = 1, slots = 1;
+  bool emulated = false, connected = false;
+  int64_t data_bytes = 0;
+  size_t region_bytes = 0;
+  char* region[kMaxRanks] = {};      // region[rank] is local; others are IPC mappings (or local in emulation)
+  bool opened[kMaxRanks] = {};
+  CommSlot* table_dev = nullptr;      // inside region[rank] (region[0] in emulation)
+  unsigned long long timeout_ns = 0;
+  int device = 0;
+};
+
+// Control region layout (byte offsets inside a rank's region).
+constexpr size_t kOffFlags = 0;                                                        // 2*512*8*4 = 32 KiB
+constexpr size_t kOffGen = kOffFlags + 2ull * kMaxCommBlocks * kMaxRanks * 4;          // 2 KiB
+constexpr size_t kOffTable = kOffGen + kMaxCommBlocks * 4;                             // 8 slots
+static_assert(kOffTable + kMaxRanks * sizeof(CommSlot) <= kCtrlBytes, "control region too small");
+
+static inline size_t round256(size_t x) { return (x + 255) & ~size_t(255); }
+
+__device__ __forceinline__ unsigned long long global_timer_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint4 ld_global16(const void* p) {
+  uint4 v;
+  asm volatile("ld.global.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+  return v;
+}
+
+// Waits until *flag has reached `gen`.  Returns false when the time limit (or the iteration cap behind
+// it) ran out.
+__device__ __forceinline__ bool wait_flag(const uint32_t* flag, uint32_t gen, unsigned long long timeout_ns) {
+  unsigned long long t0 = 0;
+  for (uint32_t it = 1; it < (1u << 26); ++it) {
+    if (static_cast<int32_t>(ld_acquire_sys(flag) - gen) >= 0) return true;
+    if ((it & 63u) == 0) {
+      const unsigned long long now = global_timer_ns();
+      if (t0 == 0) t0 = now;
+      else if (now - t0 > timeout_ns) return false;
+    }
+  }
+  return false;
+}
+
+template <typename T> struct Vec8 {
+  // eight elements of a 16-byte vector as fp32
+  static __device__ __forceinline__ void unpack(const uint4& u, float (&f)[8]) {
+    const typename Elem<T>::T2* p = reinterpret_cast<const typename Elem<T>::T2*>(&u);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float2 x = Elem<T>::to_f2(p[i]);
+      f[2 * i] = x.x;
+      f[2 * i + 1] = x.y;
+    }
+  }
+  static __device__ __forceinline__ uint4 pack(const float (&f)[8]) {
+    uint4 u;
+    typename Elem<T>::T2* p = reinterpret_cast<typename Elem<T>::T2*>(&u);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) p[i] = Elem<T>::from_f2(f[2 * i], f[2 * i + 1]);
+    return u;
+  }
+};
+
+// Sum over the block of one float per thread; every thread gets the result.  `red` holds 33 floats.
+__device__ __forceinline__ float block_sum(float v, float* red) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = (blockDim.x + 31) >> 5;
+  __syncthreads();                       // `red` may still be read by the previous row
+  if (lane == 0) red[warp] = v;
+  __syncthreads();
+  if (warp == 0) {
+    float s = lane < nwarps ? red[lane] : 0.f;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+    if (lane == 0) red[32] = s;
+  }
+  __syncthreads();
+  return red[32];
+}
+
+// ---------------------------------------------------------------------------------------------
+// all-reduce + residual + RMSNorm across ranks
+// ---------------------------------------------------------------------------------------------
+template <typename T, int VPT>
+__global__ void __launch_bounds__(1024, 1)
+allreduce_residual_rmsnorm_kernel(CommSlot* __restrict__ table, void* __restrict__ residual_base,
+                                  int64_t residual_slot_stride, const void* __restrict__ gamma_, float eps, int rows,
+                                  int hidden, unsigned long long timeout_ns, int* __restrict__ error_word) {
+  __shared__ float red[33];
+  __shared__ int s_failed;
+  CommSlot& slot = table[blockIdx.y];
+  const int rank = slot.rank, world = slot.world, blk = blockIdx.x, tid = threadIdx.x;
+  if (tid == 0) s_failed = *reinterpret_cast<volatile int*>(error_word) != 0;
+  __syncthreads();
+  if (s_failed) return;                                             // an earlier wait ran out: do nothing
+  const uint32_t gen = slot.gen[blk] + 1;
+  uint32_t* my_flags = slot.flags[rank];
+
+  // ---- barrier 1: every peer's partial sums are complete (their producer ran before this kernel in
+  // stream order; the release makes them visible to the peer that acquires the flag) ----
+  if (tid < world) {
+    if (!slot.skip_signal) st_release_sys(slot.flags[tid] + (0 * kMaxCommBlocks + blk) * kMaxRanks + rank, gen);
+    if (!wait_flag(my_flags + (0 * kMaxCommBlocks + blk) * kMaxRanks + tid, gen, timeout_ns)) {
+      atomicCAS(error_word, 0, 0x100 | tid);
+      s_failed = 1;
+    }
+  }
+  __syncthreads();
+  if (s_failed) return;
+
+  const int rows_per = (rows + world - 1) / world;
+  const int lo = min(rows, rank * rows_per), hi = min(rows, lo + rows_per);
+  const int nvec = hidden >> 3;
+  T* residual = reinterpret_cast<T*>(residual_base) + blockIdx.y * residual_slot_stride;
+  const uint4* gamma = reinterpret_cast<const uint4*>(gamma_);
+  const float inv_hidden = 1.0f / static_cast<float>(hidden);
+
+  for (int row = lo + blk; row < hi; row += gridDim.x) {
+    const size_t off = static_cast<size_t>(row) * nvec;
+    uint4 keep[VPT];
+    float ss = 0.f;
+#pragma unroll
+    for (int v = 0; v < VPT; ++v) {
+      const int c = tid + v * blockDim.x;
+      if (c < nvec) {
+        uint4 part[kMaxRanks];
+#pragma unroll
+        for (int p = 0; p < kMaxRanks; ++p)
+          if (p < world) part[p] = ld_global16(reinterpret_cast<const uint4*>(slot.in[p]) + off + c);
+        const uint4 res = reinterpret_cast<const uint4*>(residual)[static_cast<size_t>(row - lo) * nvec + c];
+        float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f}, f[8];
+#pragma unroll
+        for (int p = 0; p < kMaxRanks; ++p)
+          if (p < world) {
+            Vec8<T>::unpack(part[p], f);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) acc[i] += f[i];
+          }
+        // round the all-reduced value to the model dtype, then the residual add in that dtype: the
+        // same roundings as `all_reduce(o); residual = residual + o`
+        const uint4 o = Vec8<T>::pack(acc);
+        Vec8<T>::unpack(o, acc);
+        Vec8<T>::unpack(res, f);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) acc[i] += f[i];
+        const uint4 rn = Vec8<T>::pack(acc);
+        reinterpret_cast<uint4*>(residual)[static_cast<size_t>(row - lo) * nvec + c] = rn;
+        keep[v] = rn;
+        Vec8<T>::unpack(rn, f);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) ss += f[i] * f[i];
+      }
+    }
+    const float rstd = rsqrtf(block_sum(ss, red) * inv_hidden + eps);
+#pragma unroll
+    for (int v = 0; v < VPT; ++v) {
+      const int c = tid + v * blockDim.x;
+      if (c < nvec) {
+        float gf[8], h[8];
+        Vec8<T>::unpack(gamma[c], gf);
+        Vec8<T>::unpack(keep[v], h);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) h[i] = h[i] * rstd * gf[i];
+        const uint4 hv = Vec8<T>::pack(h);
+#pragma unroll
+        for (int p = 0; p < kMaxRanks; ++p)
+          if (p < world) {
+            const int dst = (rank + p) % world;           // spread the first stores over the links
+            st_global16(reinterpret_cast<uint4*>(slot.out[dst]) + off + c, hv);
+          }
+      }
+    }
+  }
+
+  // ---- barrier 2: every owner's rows have landed in this rank's gather buffer ----
+  __syncthreads();
+  if (tid < world) {
+    st_release_sys(slot.flags[tid] + (1 * kMaxCommBlocks + blk) * kMaxRanks + rank, gen);
+    if (!wait_flag(my_flags + (1 * kMaxCommBlocks + blk) * kMaxRanks + tid, gen, timeout_ns))
+      atomicCAS(error_word, 0, 0x200 | tid);
+  }
+  __syncthreads();
+  if (tid == 0) slot.gen[blk] = gen;
+}
+
+// ---------------------------------------------------------------------------------------------
+// local form: h = RMSNorm(x (+ residual)) for every row; the sum is stored for rows [res_lo, res_hi)
+// ---------------------------------------------------------------------------------------------
+template <typename T, int VPT>
+__global__ void __launch_bounds__(1024, 1)
+add_rmsnorm_kernel(void* __restrict__ out_, const void* __restrict__ x_, const void* residual_in_,
+                   void* residual_out_, int res_lo, int res_hi, const void* __restrict__ gamma_, float eps, int rows,
+                   int hidden) {
+  __shared__ float red[33];
+  const int tid = threadIdx.x, nvec = hidden >> 3;
+  const uint4* x = reinterpret_cast<const uint4*>(x_);
+  const uint4* rin = reinterpret_cast<const uint4*>(residual_in_);
+  uint4* rout = reinterpret_cast<uint4*>(residual_out_);
+  uint4* out = reinterpret_cast<uint4*>(out_);
+  const uint4* gamma = reinterpret_cast<const uint4*>(gamma_);
+  const float inv_hidden = 1.0f / static_cast<float>(hidden);
+  uint4 g[VPT];
+#pragma unroll
+  for (int v = 0; v < VPT; ++v) {
+    const int c = tid + v * blockDim.x;
+    g[v] = c < nvec ? gamma[c] : make_uint4(0, 0, 0, 0);
+  }
+  for (int row = blockIdx.x; row < rows; row += gridDim.x) {
+    const size_t off = static_cast<size_t>(row) * nvec;
+    const bool keep_res = rout != nullptr && row >= res_lo && row < res_hi;
+    float keep[VPT][8];
+    float ss = 0.f;
+#pragma unroll
+    for (int v = 0; v < VPT; ++v) {
+      const int c = tid + v * blockDim.x;
+      if (c < nvec) {
+        float acc[8], f[8];
+        uint4 rn = ld_stream16(x + off + c);
+        if (rin != nullptr) {
+          Vec8<T>::unpack(rn, acc);
+          Vec8<T>::unpack(rin[off + c], f);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) acc[i] += f[i];
+          rn = Vec8<T>::pack(acc);
+        }
+        if (keep_res) rout[static_cast<size_t>(row - res_lo) * nvec + c] = rn;
+        Vec8<T>::unpack(rn, keep[v]);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) ss += keep[v][i] * keep[v][i];
+      }
+    }
+    const float rstd = rsqrtf(block_sum(ss, red) * inv_hidden + eps);
+#pragma unroll
+    for (int v = 0; v < VPT; ++v) {
+      const int c = tid + v * blockDim.x;
+      if (c < nvec) {
+        float gf[8], h[8];
+        Vec8<T>::unpack(g[v], gf);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) h[i] = keep[v][i] * rstd * gf[i];
+        out[off + c] = Vec8<T>::pack(h);
+      }
+    }
+  }
+}
+
+// SwiGLU activation: out[t, j] = silu(gu[t, j]) * gu[t, inter + j], one rounding (fp32 inside).
+template <typename T>
+__global__ void __launch_bounds__(256)
+silu_mul_kernel(void* __restrict__ out_, const void* __restrict__ gu_, int64_t gu_stride, int64_t rows, int inter) {
+  const int nvec = inter >> 3;
+  const int64_t total = rows * nvec;
+  uint4* out = reinterpret_cast<uint4*>(out_);
+  const T* gu = reinterpret_cast<const T*>(gu_);
+  for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < total;
+       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const int64_t row = i / nvec;
+    const int c = static_cast<int>(i - row * nvec);
+    const T* base = gu + row * gu_stride;
+    const uint4 a = ld_stream16(reinterpret_cast<const uint4*>(base) + c);
+    const uint4 b = ld_stream16(reinterpret_cast<const uint4*>(base + inter) + c);
+    float x[8], y[8], r[8];
+    Vec8<T>::unpack(a, x);
+    Vec8<T>::unpack(b, y);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) r[k] = x[k] / (1.0f + __expf(-x[k])) * y[k];
+    out[i] = Vec8<T>::pack(r);
+  }
+}
+
+static int threads_for(int hidden, int* vpt) {
+  const int nvec = hidden / 8;
+  int threads = ((nvec + 31) / 32) * 32;
+  *vpt = 1;
+  if (threads > 1024) {
+    *vpt = 2;
+    threads = (((nvec + 1) / 2 + 31) / 32) * 32;
+  }
+  return threads;
+}
+
+// Blocks per rank: one per owned row up to what is resident at once (two 512-thread blocks per SM, one
+// larger block), since paired blocks of different ranks wait on one another.  Depends on shapes only.
+static int comm_grid(int rows, int world, int threads) {
+  const int rows_per = (rows + world - 1) / world;
+  const int cap = threads <= 512 ? kCommGridCap : kNumSMs;
+  return rows_per < 1 ? 1 : (rows_per > cap ? cap : rows_per);
+}
+
+static int cuda_fail(const char* what, cudaError_t e) {
+  cudaGetLastError();
+  return fail(MV_ERR_CUDA, "%s: %s", what, cudaGetErrorString(e));
+}
+
+static int write_table(Comm* c) {
+  CommSlot host[kMaxRanks] = {};
+  for (int s = 0; s < c->slots; ++s) {
+    const int r = c->emulated ? s : c->rank;
+    CommSlot& t = host[s];
+    for (int p = 0; p < c->world; ++p) {
+      t.in[p] = c->region[p] + kCtrlBytes;
+      t.out[p] = c->region[p] + kCtrlBytes + round256(c->data_bytes);
+      t.flags[p] = reinterpret_cast<uint32_t*>(c->region[p] + kOffFlags);
+    }
+    t.gen = reinterpret_cast<uint32_t*>(c->region[r] + kOffGen);
+    t.rank = r;
+    t.world = c->world;
+    t.skip_signal = 0;
+  }
+  const cudaError_t e = cudaMemcpy(c->table_dev, host, sizeof(CommSlot) * c->slots, cudaMemcpyHostToDevice);
+  return e == cudaSuccess ? MV_OK : cuda_fail("comm: table upload", e);
+}
+
+}  // namespace mv
+
+using namespace mv;
+
+extern "C" int64_t mv_comm_handle_bytes(void) { return static_cast<int64_t>(sizeof(cudaIpcMemHandle_t)); }
+
+extern "C" int mv_comm_create(int rank, int world, int64_t data_bytes, int timeout_ms, void** comm_out,
+                              void* handle_out) {
+  if (!comm_out || !handle_out) return fail(MV_ERR_NULL, "comm_create: null output pointer");
+  if (world < 2 || world > kMaxRanks || rank < 0 || rank >= world)
+    return fail(MV_ERR_SHAPE, "comm_create: rank %d of %d (2..%d ranks are supported)", rank, world, kMaxRanks);
+  if (data_bytes <= 0 || timeout_ms <= 0) return fail(MV_ERR_SHAPE, "comm_create: data_bytes and timeout_ms must be positive");
+  Comm* c = new (std::nothrow) Comm();
+  if (!c) return fail(MV_ERR_CUDA, "comm_create: out of host memory");
+  c->rank = rank;
+  c->world = world;
+  c->data_bytes = data_bytes;
+  c->timeout_ns = static_cast<unsigned long long>(timeout_ms) * 1000000ull;
+  c->region_bytes = kCtrlBytes + 2 * round256(static_cast<size_t>(data_bytes));
+  cudaError_t e = cudaGetDevice(&c->device);
+  if (e == cudaSuccess) e = cudaMalloc(reinterpret_cast<void**>(&c->region[rank]), c->region_bytes);
+  if (e == cudaSuccess) e = cudaMemset(c->region[rank], 0, kCtrlBytes);
+  if (e == cudaSuccess) e = cudaDeviceSynchronize();
+  cudaIpcMemHandle_t h;
+  if (e == cudaSuccess) e = cudaIpcGetMemHandle(&h, c->region[rank]);
+  if (e != cudaSuccess) {
+    if (c->region[rank]) cudaFree(c->region[rank]);
+    delete c;
+    return cuda_fail("comm_create", e);
+  }
+  memcpy(handle_out, &h, sizeof(h));
+  c->table_dev = reinterpret_cast<CommSlot*>(c->region[rank] + kOffTable);
+  *comm_out = c;
+  return MV_OK;
+}
+
+extern "C" int mv_comm_connect(void* comm, const void* all_handles) {
+  Comm* c = static_cast<Comm*>(comm);
+  if (!c || !all_handles) return fail(MV_ERR_NULL, "comm_connect: null argument");
+  if (c->emulated || c->connected) return fail(MV_ERR_SHAPE, "comm_connect: communicator is already connected");
+  const cudaIpcMemHandle_t* hs = static_cast<const cudaIpcMemHandle_t*>(all_handles);
+  for (int p = 0; p < c->world; ++p) {
+    if (p == c->rank) continue;
+    void* ptr = nullptr;
+    const cudaError_t e = cudaIpcOpenMemHandle(&ptr, hs[p], cudaIpcMemLazyEnablePeerAccess);
+    if (e != cudaSuccess) return cuda_fail("comm_connect: cudaIpcOpenMemHandle", e);
+    c->region[p] = static_cast<char*>(ptr);
+    c->opened[p] = true;
+  }
+  const int rc = write_table(c);
+  if (rc) return rc;
+  c->connected = true;
+  return MV_OK;
+}
+
+extern "C" int mv_comm_create_emulated(int world, int64_t data_bytes, int timeout_ms, void** comm_out) {
+  if (!comm_out) return fail(MV_ERR_NULL, "comm_create_emulated: null output pointer");
+  if (world < 2 || world > kMaxRanks) return fail(MV_ERR_SHAPE, "comm_create_emulated: 2..%d ranks are supported", kMaxRanks);
+  if (data_bytes <= 0 || timeout_ms <= 0) return fail(MV_ERR_SHAPE, "comm_create_emulated: data_bytes and timeout_ms must be positive");
+  Comm* c = new (std::nothrow) Comm();
+  if (!c) return fail(MV_ERR_CUDA, "comm_create_emulated: out of host memory");
+  c->world = world;
+  c->slots = world;
+  c->emulated = true;
+  c->data_bytes = data_bytes;
+  c->timeout_ns = static_cast<unsigned long long>(timeout_ms) * 1000000ull;
+  c->region_bytes = kCtrlBytes + 2 * round256(static_cast<size_t>(data_bytes));
+  cudaError_t e = cudaGetDevice(&c->device);
+  char* all = nullptr;
+  if (e == cudaSuccess) e = cudaMalloc(reinterpret_cast<void**>(&all), c->region_bytes * world);
+  if (e == cudaSuccess) e = cudaMemset(all, 0, c->region_bytes * world);
+  if (e == cudaSuccess) e = cudaDeviceSynchronize();
+  if (e != cudaSuccess) {
+    if (all) cudaFree(all);
+    delete c;
+    return cuda_fail("comm_create_emulated", e);
+  }
+  for (int p = 0; p < world; ++p) c->region[p] = all + c->region_bytes * p;
+  c->table_dev = reinterpret_cast<CommSlot*>(c->region[0] + kOffTable);
+  const int rc = write_table(c);
+  if (rc) {
+    cudaFree(all);
+    delete c;
+    return rc;
+  }
+  c->connected = true;
+  *comm_out = c;
+  return MV_OK;
+}
+
+extern "C" int mv_comm_destroy(void* comm) {
+  Comm* c = static_cast<Comm*>(comm);
+  if (!c) return MV_OK;
+  cudaDeviceSynchronize();
+  if (c->emulated) {
+    cudaFree(c->region[0]);
+  } else {
+    for (int p = 0; p < c->world; ++p)
+      if (c->opened[p]) cudaIpcCloseMemHandle(c->region[p]);
+    cudaFree(c->region[c->rank]);
+  }
+  cudaGetLastError();
+  delete c;
+  return MV_OK;
+}
+
+extern "C" void* mv_comm_input(void* comm, int slot) {
+  Comm* c = static_cast<Comm*>(comm);
+  if (!c || slot < 0 || slot >= c->slots) return nullptr;
+  return c->region[c->emulated ? slot : c->rank] + kCtrlBytes;
+}
+
+extern "C" void* mv_comm_output(void* comm, int slot) {
+  Comm* c = static_cast<Comm*>(comm);
+  if (!c || slot < 0 || slot >= c->slots) return nullptr;
+  return c->region[c->emulated ? slot : c->rank] + kCtrlBytes + round256(static_cast<size_t>(c->data_bytes));
+}
+
+// Zeroes this rank's flags and generations (every rank of an emulated communicator).  Only valid while no
+// rank has a launch in flight; every rank must reset before any rank launches again.
+extern "C" int mv_comm_reset(void* comm) {
+  Comm* c = static_cast<Comm*>(comm);
+  if (!c) return fail(MV_ERR_NULL, "comm_reset: null communicator");
+  cudaError_t e = cudaDeviceSynchronize();
+  for (int s = 0; s < c->slots && e == cudaSuccess; ++s)
+    e = cudaMemset(c->region[c->emulated ? s : c->rank], 0, kOffTable);
+  if (e == cudaSuccess) e = cudaDeviceSynchronize();
+  if (e != cudaSuccess) return cuda_fail("comm_reset", e);
+  return write_table(c);
+}
+
+// Test hook (not in the public header): the next launches of `slot` withhold their first-barrier signal, so
+// the other ranks' bounded waits run out and report through the error word.  Cleared by mv_comm_reset.
+extern "C" int mv_debug_comm_withhold_signal(void* comm, int slot) {
+  Comm* c = static_cast<Comm*>(comm);
+  if (!c || slot < 0 || slot >= c->slots) return fail(MV_ERR_SHAPE, "comm: bad slot");
+  const int one = 1;
+  const cudaError_t e = cudaMemcpy(&c->table_dev[slot].skip_signal, &one, sizeof(int), cudaMemcpyHostToDevice);
+  return e == cudaSuccess ? MV_OK : cuda_fail("comm: withhold", e);
+}
+
+template <typename T>
+static int launch_allreduce(Comm* c, void* residual, int64_t residual_slot_stride, const void* gamma, float eps, int rows,
+                            int hidden, int* error_word, cudaStream_t stream) {
+  int vpt = 1;
+  const int threads = threads_for(hidden, &vpt);
+  const dim3 grid(comm_grid(rows, c->world, threads), c->slots);
+  CommSlot* table = c->table_dev;
+  unsigned long long timeout = c->timeout_ns;
+  if (!c->emulated) {
+    if (vpt == 1)
+      allreduce_residual_rmsnorm_kernel<T, 1><<<grid, threads, 0, stream>>>(table, residual, residual_slot_stride, gamma, eps,
+                                                                            rows, hidden, timeout, error_word);
+    else
+      allreduce_residual_rmsnorm_kernel<T, 2><<<grid, threads, 0, stream>>>(table, residual, residual_slot_stride, gamma, eps,
+                                                                            rows, hidden, timeout, error_word);
+    return check_launch("allreduce_residual_rmsnorm");
+  }
+  // emulation: the blocks of all ranks wait on one another, so they must be co-resident
+  void* args[] = {&table, &residual, &residual_slot_stride, &gamma, &eps, &rows, &hidden, &timeout, &error_word};
+  const void* fn = vpt == 1 ? reinterpret_cast<const void*>(&allreduce_residual_rmsnorm_kernel<T, 1>)
+                            : reinterpret_cast<const void*>(&allreduce_residual_rmsnorm_kernel<T, 2>);
+  const cudaError_t e = cudaLaunchCooperativeKernel(fn, grid, dim3(threads), args, 0, stream);
+  if (e != cudaSuccess) return cuda_fail("allreduce_residual_rmsnorm (emulated, cooperative launch)", e);
+  return MV_OK;
+}
+
+extern "C" int mv_allreduce_residual_rmsnorm(void* comm, void* residual_shard, int64_t residual_slot_stride,
+                                             const void* gamma, float eps, int rows, int hidden, int* error_word,
+                                             int dtype, void* stream) {
+  Comm* c = static_cast<Comm*>(comm);
+  if (!c || !residual_shard || !gamma || !error_word) return fail(MV_ERR_NULL, "allreduce_residual_rmsnorm: null argument");
+  if (!c->connected) return fail(MV_ERR_SHAPE, "allreduce_residual_rmsnorm: communicator is not connected");
+  if (rows < 0 || hidden <= 0 || hidden % 8 != 0)
+    return fail(MV_ERR_SHAPE, "allreduce_residual_rmsnorm: hidden (%d) must be a positive multiple of 8, rows >= 0", hidden);
+  if (hidden > 16384) return fail(MV_ERR_LIMIT, "allreduce_residual_rmsnorm: hidden %d exceeds 16384", hidden);
+  if (static_cast<int64_t>(rows) * hidden * 2 > c->data_bytes)
+    return fail(MV_ERR_LIMIT, "allreduce_residual_rmsnorm: %d rows x %d exceed the communicator's %lld-byte buffers", rows,
+                hidden, static_cast<long long>(c->data_bytes));
+  if (!aligned16(residual_shard) || !aligned16(gamma) || (residual_slot_stride * 2) % 16 != 0)
+    return fail(MV_ERR_ALIGN, "allreduce_residual_rmsnorm: residual and gamma must be 16-byte aligned");
+  if (c->emulated) {
+    const int rows_per = (rows + c->world - 1) / c->world;
+    if (c->slots > 1 && residual_slot_stride < static_cast<int64_t>(rows_per) * hidden)
+      return fail(MV_ERR_SHAPE, "allreduce_residual_rmsnorm: residual_slot_stride smaller than one rank's shard");
+    int vpt_unused = 1;
+    if (comm_grid(rows, c->world, threads_for(hidden, &vpt_unused)) * c->slots > kNumSMs)
+      return fail(MV_ERR_LIMIT, "allreduce_residual_rmsnorm: an emulated launch is limited to %d blocks in total", kNumSMs);
+  }
+  if (rows == 0) return MV_OK;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (dtype == MV_F16) return launch_allreduce<__half>(c, residual_shard, residual_slot_stride, gamma, eps, rows, hidden, error_word, s);
+  if (dtype == MV_BF16)
+    return launch_allreduce<__nv_bfloat16>(c, residual_shard, residual_slot_stride, gamma, eps, rows, hidden, error_word, s);
+  return fail(MV_ERR_DTYPE, "allreduce_residual_rmsnorm: dtype %d", dtype);
+}
+
+extern "C" int mv_add_rmsnorm(void* out, const void* x, const void* residual_in, void* residual_out, int64_t res_lo,
+                              int64_t res_hi, const void* gamma, float eps, int64_t rows, int hidden, int dtype,
+                              void* stream) {
+  if (!out || !x || !gamma) return fail(MV_ERR_NULL, "add_rmsnorm: null argument");
+  if (rows < 0 || rows > 0x7fffffff || hidden <= 0 || hidden % 8 != 0)
+    return fail(MV_ERR_SHAPE, "add_rmsnorm: hidden (%d) must be a positive multiple of 8, 0 <= rows < 2^31", hidden);
+  if (hidden > 16384) return fail(MV_ERR_LIMIT, "add_rmsnorm: hidden %d exceeds 16384", hidden);
+  if (!aligned16(out) || !aligned16(x) || !aligned16(gamma) || !aligned16(residual_in) || !aligned16(residual_out))
+    return fail(MV_ERR_ALIGN, "add_rmsnorm: pointers must be 16-byte aligned");
+  if (residual_out && (res_lo < 0 || res_hi < res_lo || res_hi > rows))
+    return fail(MV_ERR_SHAPE, "add_rmsnorm: residual row range [%lld, %lld) outside [0, %lld)", (long long)res_lo,
+                (long long)res_hi, (long long)rows);
+  if (rows == 0) return MV_OK;
+  int vpt = 1;
+  const int threads = threads_for(hidden, &vpt);
+  const int grid = static_cast<int>(rows < 8 * kNumSMs ? rows : 8 * kNumSMs);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const int lo = static_cast<int>(res_lo), hi = static_cast<int>(res_hi), r = static_cast<int>(rows);
+#define MV_LAUNCH_ADD_NORM(T, V) \
+  add_rmsnorm_kernel<T, V><<<grid, threads, 0, s>>>(out, x, residual_in, residual_out, lo, hi, gamma, eps, r, hidden)
+  if (dtype == MV_F16) {
+    if (vpt == 1) MV_LAUNCH_ADD_NORM(__half, 1); else MV_LAUNCH_ADD_NORM(__half, 2);
+  } else if (dtype == MV_BF16) {
+    if (vpt == 1) MV_LAUNCH_ADD_NORM(__nv_bfloat16, 1); else MV_LAUNCH_ADD_NORM(__nv_bfloat16, 2);
+  } else {
+    return fail(MV_ERR_DTYPE, "add_rmsnorm: dtype %d", dtype);
+  }
+#undef MV_LAUNCH_ADD_NORM
+  return check_launch("add_rmsnorm");
+}
+
+extern "C" int mv_silu_mul(void* out, const void* gate_up, int64_t gate_up_stride, int64_t rows, int inter, int dtype,
+                           void* stream) {
+  if (!out || !gate_up) return fail(MV_ERR_NULL, "silu_mul: null argument");
+  if (rows < 0 || inter <= 0 || inter % 8 != 0 || gate_up_stride < 2ll * inter || gate_up_stride % 8 != 0)
+    return fail(MV_ERR_SHAPE, "silu_mul: inter (%d) must be a positive multiple of 8 and the row stride a multiple of 8 >= 2*inter", inter);
+  if (!aligned16(out) || !aligned16(gate_up)) return fail(MV_ERR_ALIGN, "silu_mul: pointers must be 16-byte aligned");
+  if (rows == 0) return MV_OK;
+  const int64_t total = rows * (inter / 8);
+  const int64_t want = (total + 255) / 256;
+  const int grid = static_cast<int>(want < 16 * kNumSMs ? want : 16 * kNumSMs);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (dtype == MV_F16) silu_mul_kernel<__half><<<grid, 256, 0, s>>>(out, gate_up, gate_up_stride, rows, inter);
+  else if (dtype == MV_BF16) silu_mul_kernel<__nv_bfloat16><<<grid, 256, 0, s>>>(out, gate_up, gate_up_stride, rows, inter);
+  else return fail(MV_ERR_DTYPE, "silu_mul: dtype %d", dtype);
+  return check_launch("silu_mul");
+}

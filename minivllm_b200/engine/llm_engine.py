@@ -35,6 +35,14 @@ class LLMEngine:
         self.scheduler.add_sequence(seq)
         return seq
 
+    def _account(self, seqs, is_prefill, dt):
+        n = sum(len(s) - 1 - s.num_cached_tokens for s in seqs) if is_prefill else len(seqs)
+        key = "prefill" if is_prefill else "decode"
+        self.stats[key + "_tokens"] += n
+        self.stats[key + "_s"] += dt
+        self.stats["steps"] += 1
+        return n
+
     def step(self):
         seqs, is_prefill = self.scheduler.schedule()
         if not seqs:
@@ -43,21 +51,51 @@ class LLMEngine:
         tokens = self.model_runner.run(seqs, is_prefill)
         dt = time.perf_counter() - t0
         self.scheduler.postprocess(seqs, tokens)
-        n = sum(len(s) - 1 - s.num_cached_tokens for s in seqs) if is_prefill else len(seqs)
-        key = "prefill" if is_prefill else "decode"
-        self.stats[key + "_tokens"] += n
-        self.stats[key + "_s"] += dt
-        self.stats["steps"] += 1
+        n = self._account(seqs, is_prefill, dt)
         done = [(s.seq_id, s.completion_token_ids) for s in seqs if s.is_finished]
         return done, n, is_prefill
 
     def generate(self, prompts, sampling_params: SamplingParams = None):
-        """prompts: list of token-id lists.  Returns {'token_ids': completions in submission order}."""
+        """prompts: list of token-id lists.  Returns {'token_ids': completions in submission order}.
+
+        The loop keeps one step in flight: when no sequence of a batch can stop on an EOS token, the next step
+        is scheduled and launched (lengths and finishes are known from counts; the last token of every
+        sequence already sits in device memory) before the previous step's sampled tokens are read back, so
+        the device->host read and the host bookkeeping overlap the GPU work."""
         seqs = [self.add_prompt(p, sampling_params) for p in prompts]
-        while not self.scheduler.is_finished():
-            done, n, _ = self.step()
-            if n == 0 and not done:
+        sch, runner = self.scheduler, self.model_runner
+        lookahead = self.config.get("lookahead", True)
+        pending = None                       # (handle, seqs, positions) of the step in flight
+        t_last = time.perf_counter()
+
+        def resolve():
+            nonlocal pending
+            if pending is not None:
+                handle, pseqs, at = pending
+                sch.fill_tokens(pseqs, at, runner.finish(handle))
+                pending = None
+
+        while not sch.is_finished():
+            if pending is not None and not sch.no_preemption_next():
+                resolve()
+            batch, is_prefill = sch.schedule()
+            if not batch:
+                resolve()
+                if sch.is_finished():
+                    break
                 raise RuntimeError("scheduler made no progress: the KV pool cannot hold a single request")
+            handle = runner.launch(batch, is_prefill)
+            if lookahead and sch.can_run_ahead(batch):
+                at = sch.advance(batch)
+                resolve()                    # the previous step, while this one runs
+                pending = (handle, batch, at)
+            else:
+                resolve()
+                sch.postprocess(batch, runner.finish(handle))
+            now = time.perf_counter()
+            self._account(batch, is_prefill, now - t_last)
+            t_last = now
+        resolve()
         return {"token_ids": [s.completion_token_ids for s in seqs]}
 
     def exit(self):

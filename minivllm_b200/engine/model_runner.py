@@ -21,6 +21,7 @@ import math
 import torch
 import torch.distributed as dist
 
+from ..layers.attention import _error_word
 from ..utils.context import get_context, reset_context, set_context
 from .metadata import SequenceStateTable
 from ..layers.sampler import greedy_tokens
@@ -53,6 +54,10 @@ class ModelRunner:
         self.model = model if model is not None else Qwen3ForCausalLM(
             mcfg, tp_rank=rank, tp_size=self.world_size, dtype=self.dtype, device=self.device,
             seed=config.get("seed", 0))
+        self.comm, self.comm_note = None, "single rank"
+        if self.world_size > 1:
+            self._attach_communicator()
+        self.error_word = _error_word(self.device)
         self.max_blocks_per_seq = math.ceil(self.max_model_len / self.block_size)
         # one spare slot: padded rows of a captured batch point at it
         self.num_slots = self.max_num_seqs + 1
@@ -62,6 +67,8 @@ class ModelRunner:
         torch.cuda.manual_seed(config.get("sample_seed", 1234))
         self.graphs, self.graph_vars = {}, None
         self.decode_workspace = None
+        self._stage, self._stage_at, self._stage_dev = None, 0, None
+        self._readback, self._readback_at = None, 0
         self.allocate_kv_cache()
         if not self.enforce_eager:
             self.capture_cudagraph()
@@ -139,12 +146,47 @@ class ModelRunner:
                     last_token_index=meta["last_token_index"])
         return input_ids
 
+    def _attach_communicator(self):
+        """The fused all-reduce + residual + RMSNorm over NVLink peer memory (layers/allreduce.py) replaces the
+        NCCL all-reduces of the model.  If the peer mapping cannot be set up (every rank learns it at the same
+        point), the model keeps NCCL and says so in `comm_note`."""
+        if not self.config.get("custom_allreduce", True):
+            self.comm_note = "NCCL all-reduce (custom_allreduce=False)"
+            return
+        from ..layers.allreduce import TPCommunicator
+        err, comm = "", None
+        try:
+            comm = TPCommunicator(self.rank, self.world_size, self.max_num_batched_tokens, self.model_cfg.hidden_size,
+                                  self.dtype, self.device, timeout_ms=self.config.get("comm_timeout_ms", 5000))
+        except Exception as e:  # noqa: BLE001 - reported, and agreed on by all ranks below
+            err = f"{type(e).__name__}: {e}"
+        ok = torch.tensor([0 if err else 1], device=self.device, dtype=torch.int32)
+        dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+        if int(ok.item()) == 1:
+            self.comm, self.model.comm = comm, comm
+            self.comm_note = "fused all-reduce + residual + RMSNorm kernel over NVLink peer memory"
+        else:
+            if comm is not None:
+                comm.close()
+            self.comm_note = "NCCL all-reduce (peer-memory communicator unavailable: %s)" % (err or "failed on another rank")
+            if self.rank == 0:
+                print("minivllm_b200: " + self.comm_note, flush=True)
+
     def _upload_slots(self, seqs, slots_buf, n_active_buf):
+        """Slot ids of the batch (padding rows point at the spare slot) and the live count: one pinned staging
+        row out of a small ring, one H2D copy."""
         bp = slots_buf.shape[0]
-        host = torch.full((bp + 1,), self.pad_slot, dtype=torch.int32)
-        host[:len(seqs)] = torch.tensor([s.slot for s in seqs], dtype=torch.int32)
-        host[bp] = len(seqs)
-        dev = host.pin_memory().to(self.device, non_blocking=True)
+        if self._stage is None:
+            self._stage = [torch.empty(self.max_num_seqs + 1, dtype=torch.int32).pin_memory() for _ in range(4)]
+            self._stage_dev = torch.empty(self.max_num_seqs + 1, dtype=torch.int32, device=self.device)
+        host = self._stage[self._stage_at % len(self._stage)]
+        self._stage_at += 1
+        n = len(seqs)
+        host[:n] = torch.tensor([s.slot for s in seqs], dtype=torch.int32)
+        host[n:bp] = self.pad_slot
+        host[bp] = n
+        dev = self._stage_dev[:bp + 1]
+        dev.copy_(host[:bp + 1], non_blocking=True)
         slots_buf.copy_(dev[:bp])
         n_active_buf.copy_(dev[bp:])
 
@@ -191,27 +233,56 @@ class ModelRunner:
         """Hidden states of the rows that get a next token (last token of each sequence in prefill)."""
         return self.model(input_ids)
 
-    @torch.inference_mode()
     def run(self, seqs, is_prefill):
+        """One model step, synchronously: sampled token ids of `seqs` as a Python list."""
+        return self.finish(self.launch(seqs, is_prefill))
+
+    @torch.inference_mode()
+    def launch(self, seqs, is_prefill):
+        """Enqueues one model step and the device->host copy of its result; returns a handle for `finish`.
+        Nothing here waits for the GPU."""
         temps = None
         if not self.greedy:
             temps = torch.tensor([s.temperature for s in seqs], dtype=torch.float32).pin_memory().to(
                 self.device, non_blocking=True)
+        n = len(seqs)
         if is_prefill:
             input_ids = self.prepare_prefill(seqs)
             tokens = self.next_tokens(self.run_model(input_ids, True), temps)
             slots = torch.tensor([s.slot for s in seqs], dtype=torch.int64).pin_memory().to(self.device,
                                                                                              non_blocking=True)
             self.state.last_token.index_copy_(0, slots, tokens)
+            result = torch.cat([tokens, self.error_word.to(torch.int64)])
         elif self.enforce_eager or not self.graphs:
             input_ids, slots_buf = self.prepare_decode(seqs)
             tokens = self.next_tokens(self.run_model(input_ids, False), temps)
             self.state.last_token.index_copy_(0, slots_buf.long(), tokens)
+            result = torch.cat([tokens, self.error_word.to(torch.int64)])
         else:
-            tokens = self._replay(seqs, temps)
-        out = tokens[:len(seqs)].tolist()          # the step's only device->host read
+            result = self._replay(seqs, temps)      # (max_num_seqs + 1,): tokens, then the error word
         reset_context()
-        return out
+        if self._readback is None:
+            self._readback = [torch.empty(max(self.max_num_seqs, self.max_num_batched_tokens) + 1,
+                                          dtype=torch.int64).pin_memory() for _ in range(4)]
+        host = self._readback[self._readback_at % len(self._readback)][:result.numel()]
+        self._readback_at += 1
+        host.copy_(result, non_blocking=True)        # the step's only device->host read
+        done = torch.cuda.Event()
+        done.record()
+        return host, done, n
+
+    def finish(self, handle):
+        """Waits for a launched step; raises if a kernel wait of the step ran out of time."""
+        host, done, n = handle
+        done.synchronize()
+        code = int(host[-1])
+        if code:
+            self.error_word.zero_()
+            raise RuntimeError(
+                f"a bounded wait inside a kernel ran out of time (error word {code:#x}): "
+                + ("a tensor-parallel peer did not arrive; the communicator must be reset on every rank"
+                   if code >= 0x100 else "prefill attention pipeline") + "; the step's tokens are not valid")
+        return host[:n].tolist()
 
     # ------------------------------------------------------------------ graphs ---
     def _decode_body(self, v, bp):
@@ -221,6 +292,7 @@ class ModelRunner:
         self._set_decode_context(bufs)
         tokens = self.next_tokens(self.model(bufs["input_ids"]), None if self.greedy else v["temps"][:bp])
         v["tokens"][:bp].copy_(tokens)
+        v["tokens"][self.max_num_seqs:].copy_(self.error_word)
         self.state.last_token.index_copy_(0, v["slots"][:bp].long(), tokens)
 
     @torch.inference_mode()
@@ -230,7 +302,7 @@ class ModelRunner:
                  slots=torch.full((max_bs,), self.pad_slot, dtype=torch.int32, device=self.device),
                  n_active=torch.zeros(1, dtype=torch.int32, device=self.device),
                  temps=torch.ones(max_bs, dtype=torch.float32, device=self.device),
-                 tokens=torch.zeros(max_bs, dtype=torch.int64, device=self.device))
+                 tokens=torch.zeros(max_bs + 1, dtype=torch.int64, device=self.device))
         c = self.model_cfg
         from .. import _cabi
         need = _cabi.lib().mv_paged_decode_workspace_bytes(max_bs, c.num_heads // self.world_size,
@@ -265,5 +337,12 @@ class ModelRunner:
         return v["tokens"]
 
     def exit(self):
+        torch.cuda.synchronize()
         self.graphs, self.graph_vars = {}, None
+        if self.comm is not None:
+            self.model.comm = None
+            if self.world_size > 1:
+                dist.barrier()           # no rank unmaps while a peer may still be inside a kernel
+            self.comm.close()
+            self.comm = None
         torch.cuda.synchronize()

@@ -12,7 +12,11 @@ to fp32 and then fails in o_proj); positions come from the Context, built once
 per step on the GPU (the reference rebuilds them on the host in every layer);
 weights are seeded (the reference leaves them uninitialised).  Kept as in the
 reference: RMSNorm eps 1e-5 whatever the config says, one shared gamma for the
-q and k norms, tied embeddings when asked.
+q and k norms, tied embeddings when asked, and a residual stream that starts
+from the normalised embedding (models/qwen3.py:186-190).  On CUDA the residual
+adds, norms, SwiGLU activation and (under tensor parallelism) the all-reduces
+run through the fused kernels of layers/layernorm.py, layers/activation.py and
+layers/allreduce.py; CPU tensors take the plain torch formulation.
 """
 import math
 from dataclasses import dataclass
@@ -21,7 +25,10 @@ import torch
 import torch.nn as nn
 import torch.nn.functional as F
 
+from ..layers.activation import silu_and_mul
+from ..layers.allreduce import shard_rows
 from ..layers.attention import Attention, qk_norm_rope_store
+from ..layers.layernorm import add_rms_norm
 from ..utils.context import get_context
 
 RMS_EPS = 1e-5
@@ -116,17 +123,21 @@ class DecoderLayer(nn.Module):
         self.fused_pre_attention = cfg.fused_pre_attention and D == 128 and torch.device(device).type == "cuda"
 
     def forward(self, x, residual, cos, sin, rope=None):
-        residual = x if residual is None else residual + x
-        h = F.rms_norm(residual, (residual.shape[-1],), self.input_norm_w, RMS_EPS)
+        """Plain torch formulation (the reference's layer structure, src/myvllm/models/qwen3.py:186-217): the
+        path of CPU tensors, i.e. of the tests and the CPU baseline that drive this harness with the oracle's
+        attention.  CUDA tensors take `forward_fused`."""
+        if residual is None:
+            # first layer, as the reference has it (models/qwen3.py:186-190): the residual stream starts from
+            # the NORMALISED embedding, not from the embedding itself
+            h = F.rms_norm(x, (x.shape[-1],), self.input_norm_w, RMS_EPS)
+            residual = h
+        else:
+            residual = residual + x
+            h = F.rms_norm(residual, (residual.shape[-1],), self.input_norm_w, RMS_EPS)
         qkv = F.linear(h, self.qkv_w)
         v = qkv[:, (self.h + self.kvh) * self.d:].view(-1, self.kvh, self.d)   # v stays a strided view of qkv
         if self.fused_pre_attention:
-            # one launch: q/k RMSNorm + RoPE + the K/V scatter into the paged cache
-            ctx = get_context()
-            a = self.attn
-            q, k = qk_norm_rope_store(qkv, ctx.positions, rope[0], rope[1], self.qk_norm_w, self.qk_norm_w, RMS_EPS,
-                                      self.h, self.kvh, self.d, a.k_cache, a.v_cache, ctx.slot_mapping)
-            o = a(q, k, v, store=False)
+            o = self._attention_fused(qkv, v, rope)
         else:
             q, k, _ = qkv.split([self.h * self.d, self.kvh * self.d, self.kvh * self.d], dim=-1)
             q = F.rms_norm(q.reshape(-1, self.h, self.d), (self.d,), self.qk_norm_w, RMS_EPS)
@@ -145,11 +156,46 @@ class DecoderLayer(nn.Module):
             torch.distributed.all_reduce(out)
         return out, residual
 
+    def _attention_fused(self, qkv, v, rope):
+        # one launch: q/k RMSNorm + RoPE + the K/V scatter into the paged cache
+        ctx = get_context()
+        a = self.attn
+        q, k = qk_norm_rope_store(qkv, ctx.positions, rope[0], rope[1], self.qk_norm_w, self.qk_norm_w, RMS_EPS,
+                                  self.h, self.kvh, self.d, a.k_cache, a.v_cache, ctx.slot_mapping)
+        return a(q, k, v, store=False)
+
+    def _reduce_add_norm(self, partial, residual, gamma, comm):
+        """All-reduce of the row-parallel partial sums + residual add + RMSNorm with `gamma`.
+        With a communicator: one kernel over NVLink peer memory; `partial` is the communicator's input buffer and
+        `residual` this rank's row shard.  Without: NCCL (when sharded) and the local fused add + norm on the
+        replicated residual.  Returns the normalised activations of ALL rows; `residual` is updated in place."""
+        if comm is not None:
+            return comm.allreduce_residual_rmsnorm(partial.shape[0], residual, gamma, RMS_EPS)
+        if self.tp_size > 1:
+            torch.distributed.all_reduce(partial)
+        return add_rms_norm(partial, residual, gamma, RMS_EPS, residual_out=residual)
+
+    def forward_fused(self, h, residual, next_gamma, rope, comm=None):
+        """CUDA path.  `h` = normalised input of this layer (all rows), `residual` = the residual stream (this
+        rank's row shard when `comm` is set, all rows otherwise), `next_gamma` = weight of the norm that follows
+        this layer (next layer's input norm, or the final norm).  Returns the next layer's normalised input."""
+        rows = h.shape[0]
+        qkv = F.linear(h, self.qkv_w)
+        v = qkv[:, (self.h + self.kvh) * self.d:].view(-1, self.kvh, self.d)
+        o = self._attention_fused(qkv, v, rope)
+        partial = torch.mm(o, self.o_w.t(), out=comm.input_rows(rows)) if comm is not None else F.linear(o, self.o_w)
+        h = self._reduce_add_norm(partial, residual, self.post_norm_w, comm)
+        act = silu_and_mul(F.linear(h, self.gate_up_w))
+        partial = torch.mm(act, self.down_w.t(), out=comm.input_rows(rows)) if comm is not None else \
+            F.linear(act, self.down_w)
+        return self._reduce_add_norm(partial, residual, next_gamma, comm)
+
 
 class Qwen3ForCausalLM(nn.Module):
     def __init__(self, cfg: Qwen3Config, tp_rank=0, tp_size=1, dtype=torch.bfloat16, device="cuda", seed=0):
         super().__init__()
-        self.cfg, self.tp_size, self.dtype = cfg, tp_size, dtype
+        self.cfg, self.tp_size, self.tp_rank, self.dtype = cfg, tp_size, tp_rank, dtype
+        self.comm = None   # layers.allreduce.TPCommunicator, attached by the model runner under tensor parallelism
         self.embed = nn.Parameter(_seeded_normal((cfg.vocab_size, cfg.hidden_size), seed * 1000003 + 900001,
                                                  device).to(dtype), requires_grad=False)
         if cfg.tie_word_embeddings:
@@ -170,11 +216,29 @@ class Qwen3ForCausalLM(nn.Module):
         if positions is None:
             raise ValueError("Context.positions must be set before the model runs")
         fused = all(l.fused_pre_attention for l in self.layers)
+        x = F.embedding(input_ids, self.embed)
+        if fused and x.is_cuda:
+            return self._forward_fused(x)
         cos, sin = (None, None) if fused else (self.rope_cos[positions], self.rope_sin[positions])
-        x, residual = F.embedding(input_ids, self.embed), None
+        residual = None
         for layer in self.layers:
             x, residual = layer(x, residual, cos, sin, (self.rope_cos, self.rope_sin))
         return F.rms_norm(residual + x, (x.shape[-1],), self.final_norm_w, RMS_EPS)
+
+    def _forward_fused(self, x):
+        """Every norm is fused with the add (and, under tensor parallelism, the all-reduce) in front of it, so a
+        layer hands the next one its normalised input; with a communicator the residual stream is sharded by
+        rows and never replicated."""
+        rows = x.shape[0]
+        comm = self.comm if self.comm is not None and rows <= self.comm.max_rows else None
+        lo, hi = shard_rows(rows, self.tp_rank, self.tp_size) if comm is not None else (0, rows)
+        h = add_rms_norm(x, None, self.layers[0].input_norm_w, RMS_EPS)
+        residual = h[lo:hi].clone()      # the reference starts the residual stream from the normalised embedding
+        rope = (self.rope_cos, self.rope_sin)
+        for i, layer in enumerate(self.layers):
+            nxt = self.layers[i + 1].input_norm_w if i + 1 < len(self.layers) else self.final_norm_w
+            h = layer.forward_fused(h, residual, nxt, rope, comm)
+        return h
 
     def compute_logits(self, hidden, vocab_shard=None):
         """Prefill keeps the last token of every sequence (Context.last_token_index); decode keeps all rows.

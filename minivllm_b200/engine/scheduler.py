@@ -67,6 +67,36 @@ class Scheduler:
         for seq, tok in zip(seqs, token_ids):
             seq.append_token(tok)
             if (not seq.ignore_eos and tok == self.eos) or seq.num_completion_tokens >= seq.max_tokens:
-                seq.status = SequenceStatus.FINISHED
-                self.block_manager.deallocate(seq)
-                self.running.remove(seq)
+                self._finish(seq)
+
+    def _finish(self, seq):
+        seq.status = SequenceStatus.FINISHED
+        self.block_manager.deallocate(seq)
+        self.running.remove(seq)
+
+    # ---- one step of lookahead: bookkeeping before the sampled tokens have reached the host ----
+    def can_run_ahead(self, seqs):
+        """True when the step after this one can be scheduled without knowing this step's tokens: no
+        sequence of the batch can end on an EOS token, and no token value is hashed (prefix cache off)."""
+        return not self.block_manager.prefix_caching and all(s.ignore_eos or self.eos < 0 for s in seqs)
+
+    def no_preemption_next(self):
+        """The next decode step finds a block for every running sequence, so nothing is preempted (a preempted
+        sequence is prefilled again from its token ids, which must then be real)."""
+        return len(self.block_manager.free_blocks) >= len(self.running)
+
+    def advance(self, seqs):
+        """postprocess() with the token values still unknown: appends a placeholder to every sequence and
+        finishes those that reached max_tokens.  Returns the positions to hand to `fill_tokens`."""
+        at = []
+        for seq in seqs:
+            at.append(len(seq.token_ids))
+            seq.append_token(-1)
+            if seq.num_completion_tokens >= seq.max_tokens:
+                self._finish(seq)
+        return at
+
+    @staticmethod
+    def fill_tokens(seqs, positions, token_ids):
+        for seq, pos, tok in zip(seqs, positions, token_ids):
+            seq.token_ids[pos] = int(tok)
