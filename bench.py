@@ -39,8 +39,9 @@ sys.path.insert(0, ROOT)
 
 from minivllm_b200 import synth  # noqa: E402
 
-# dram__bytes_read+write / algorithmic bytes of paged_decode_kernel, from the ncu capture summarised in
-# profiles/paged_decode_fp16_b64_ctx1024-4096.md (traffic grows in proportion to the KV tokens read)
+# dram__bytes_read+write / algorithmic bytes of paged_decode_kernel in an ncu capture of the batch-64 case
+# (`--workload decode --small`: 652.4 MB measured against 652.1 MB algorithmic); traffic grows in proportion to
+# the KV tokens read, so the ratio carries over to the larger cases that are too big to capture
 NCU_TRAFFIC_RATIO = 652.4 / 652.1
 
 
@@ -229,59 +230,230 @@ def _time_calls(fns, iters, warmup=5):
     return a.elapsed_time(b) / iters
 
 
-def extras(device, pk):
-    """Secondary numbers of the same run: the exact small decode configuration and store_kvcache."""
+def _graph_timed(fn, calls=20, replays=10):
+    """Per-call device time (ms) of `fn` replayed inside a CUDA graph: no host work between launches."""
+    s = torch.cuda.Stream()
+    s.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(s):
+        fn()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=s):
+            for _ in range(calls):
+                fn()
+    torch.cuda.current_stream().wait_stream(s)
+    return _time_calls([g.replay], replays, 3) / calls
+
+
+def _hbm(ms, nbytes, pk, **more):
+    d = {"us_per_call": ms * 1e3, "GBps": nbytes / ms / 1e6, "frac_of_measured_peak": nbytes / ms / 1e6 / pk["hbm_gbs"],
+         "bytes": nbytes}
+    d.update(more)
+    return d
+
+
+def case_decode_cfg0(device, pk, iters=200):
+    """Paged decode, the exact small configuration: batch 16, ctx [64,1024], 16q/8kv, fp16 (34 MB of KV fits L2:
+    8 rotating cache copies).  Timed through the Python operator and, launch-only, inside a CUDA graph."""
     from minivllm_b200.layers import attention as A
-    out = {}
-    # decode, exact configuration: batch 16, ctx [64,1024] (34 MB of KV, fits L2) -> rotate 8 cache copies
     d = synth.decode_inputs(seed=0)
     dt = torch.float16
     q, bt, cl = d["q"].to(dt).to(device), d["block_tables"].to(device), d["context_lens"].to(device)
     copies = [(d["k_cache"].to(dt).to(device).clone(), d["v_cache"].to(dt).to(device).clone()) for _ in range(8)]
     fns = [lambda kc=kc, vc=vc: A.paged_attention_decode(q, kc, vc, bt, cl, d["scale"], 16, 8, 128, 256)
            for kc, vc in copies]
-    ms = _time_calls(fns, 200, 20)
+    ms = _time_calls(fns, iters, 20)
     nbytes = synth.decode_bytes(d["context_lens"], 16, 16, 8, 128, 2, bt.shape[1])
-    out["decode_batch16_ctx64_1024"] = {"us_per_call": ms * 1e3, "GBps": nbytes / ms / 1e6,
-                                        "frac_of_measured_peak": nbytes / ms / 1e6 / pk["hbm_gbs"],
-                                        "l2": "8 rotating cache copies (272 MB)", "bytes": nbytes}
-    del copies, fns
-    # store_kvcache: 65,536 tokens, 8 kv heads x 128, bf16, 4096 x 256-slot cache, ~3% padding
+    state = {"i": 0}
+
+    def rotate():
+        fns[state["i"] % 8]()
+        state["i"] += 1
+    msg = _graph_timed(rotate, calls=16, replays=max(2, iters // 16))
+    return _hbm(ms, nbytes, pk, l2="8 rotating cache copies (272 MB)", us_per_call_in_graph=msg * 1e3,
+                GBps_in_graph=nbytes / msg / 1e6)
+
+
+def case_decode_tp8_shape(device, pk, iters=20):
+    """Paged decode at the per-rank shape of the engine under TP=8: batch 512, 4 q heads / 1 kv head, ctx
+    uniform[768,1792] (prompt + 256), bf16, 256-token blocks (1.3 GB of KV per call)."""
+    from minivllm_b200.layers import attention as A
+    d = synth.decode_inputs(seed=4, batch=512, ctx_lo=768, ctx_hi=1792, num_heads=4, num_kv_heads=1)
+    dt = torch.bfloat16
+    q, bt, cl = d["q"].to(dt).to(device), d["block_tables"].to(device), d["context_lens"].to(device)
+    kc, vc = d["k_cache"].to(dt).to(device), d["v_cache"].to(dt).to(device)
+    ms = _time_calls([lambda: A.paged_attention_decode(q, kc, vc, bt, cl, d["scale"], 4, 1, 128, 256)], iters, 3)
+    return _hbm(ms, synth.decode_bytes(d["context_lens"], 512, 4, 1, 128, 2, bt.shape[1]), pk)
+
+
+def case_decode_int8(device, pk, iters=20):
+    """Paged decode from an int8 cache (fp16 scales): batch 64, ctx [1024,4096], 16q/8kv, fp16 queries."""
+    from minivllm_b200.layers import attention as A
+    d = synth.decode_inputs(seed=3, batch=64, ctx_lo=1024, ctx_hi=4096, num_heads=16, num_kv_heads=8)
+    nb, bs, kvh, hd = d["k_cache"].shape
+    dt = torch.float16
+    kq, vq = (torch.zeros(nb, bs, kvh, hd, dtype=torch.int8, device=device) for _ in range(2))
+    ks, vs = (torch.zeros(nb, bs, kvh, dtype=torch.float16, device=device) for _ in range(2))
+    slots = torch.arange(nb * bs, dtype=torch.int64, device=device)
+    A.store_kvcache(d["k_cache"].reshape(-1, kvh, hd).to(dt).to(device), d["v_cache"].reshape(-1, kvh, hd).to(dt).to(device),
+                    kq, vq, slots, bs, k_scale=ks, v_scale=vs)
+    q, bt, cl = d["q"].to(dt).to(device), d["block_tables"].to(device), d["context_lens"].to(device)
+    ms = _time_calls([lambda: A.paged_attention_decode(q, kq, vq, bt, cl, d["scale"], 16, 8, 128, 256, k_scale=ks,
+                                                       v_scale=vs)], iters, 3)
+    return _hbm(ms, synth.decode_bytes(d["context_lens"], 64, 16, 8, 128, 2, bt.shape[1], int8=True), pk)
+
+
+def case_store(device, pk, iters=50, int8=False):
+    """store_kvcache: 65,536 tokens, 8 kv heads x 128, bf16, 4096 x 256-slot cache, ~3 % padding slots."""
+    from minivllm_b200.layers import attention as A
     s = synth.store_inputs()
     bf = torch.bfloat16
     slots = s["slot_mapping"].to(device)
     valid = int((s["slot_mapping"] >= 0).sum())
     shape = (s["num_blocks"], s["block_size"], 8, 128)
-    kc, vc = torch.zeros(shape, dtype=bf, device=device), torch.zeros(shape, dtype=bf, device=device)
     srcs = [(s["k"].to(bf).to(device).clone(), s["v"].to(bf).to(device).clone()) for _ in range(2)]
-    fns = [lambda k=k, v=v: A.store_kvcache(k, v, kc, vc, slots, 256) for k, v in srcs]
-    ms = _time_calls(fns, 50)
-    nbytes = valid * 8 * 128 * (2 * 2 + 2 * 2) + 65536 * 8
-    out["store_kvcache_bf16"] = {"us_per_call": ms * 1e3, "GBps": nbytes / ms / 1e6,
-                                 "frac_of_measured_peak": nbytes / ms / 1e6 / pk["hbm_gbs"], "bytes": nbytes}
-    del kc, vc
-    kq, vq = torch.zeros(shape, dtype=torch.int8, device=device), torch.zeros(shape, dtype=torch.int8, device=device)
-    ks = torch.zeros(shape[:3], dtype=torch.float16, device=device)
-    vs = torch.zeros(shape[:3], dtype=torch.float16, device=device)
-    fns = [lambda k=k, v=v: A.store_kvcache(k, v, kq, vq, slots, 256, k_scale=ks, v_scale=vs) for k, v in srcs]
-    ms = _time_calls(fns, 50)
-    nbytes = valid * 8 * (128 * (2 * 2 + 2 * 1) + 2 * 2) + 65536 * 8
-    out["store_kvcache_int8"] = {"us_per_call": ms * 1e3, "GBps": nbytes / ms / 1e6,
-                                 "frac_of_measured_peak": nbytes / ms / 1e6 / pk["hbm_gbs"], "bytes": nbytes}
-    del kq, vq, ks, vs, srcs, fns
-    # varlen causal prefill: 32 sequences, lengths [128,2048], 32 q / 8 kv heads, head_dim 128, bf16
-    p = synth.prefill_inputs()
+    if int8:
+        kq, vq = (torch.zeros(shape, dtype=torch.int8, device=device) for _ in range(2))
+        ks, vs = (torch.zeros(shape[:3], dtype=torch.float16, device=device) for _ in range(2))
+        fns = [lambda k=k, v=v: A.store_kvcache(k, v, kq, vq, slots, 256, k_scale=ks, v_scale=vs) for k, v in srcs]
+        nbytes = valid * 8 * (128 * (2 * 2 + 2 * 1) + 2 * 2) + 65536 * 8
+    else:
+        kc, vc = torch.zeros(shape, dtype=bf, device=device), torch.zeros(shape, dtype=bf, device=device)
+        fns = [lambda k=k, v=v: A.store_kvcache(k, v, kc, vc, slots, 256) for k, v in srcs]
+        nbytes = valid * 8 * 128 * (2 * 2 + 2 * 2) + 65536 * 8
+    return _hbm(_time_calls(fns, iters, 3), nbytes, pk)
+
+
+def case_prefill(device, pk, iters=20, num_seqs=32, len_lo=128, len_hi=2048):
+    """Varlen causal prefill: 32 sequences, lengths [128,2048], 32 q / 8 kv heads, head_dim 128, bf16."""
+    from minivllm_b200.layers import attention as A
+    p = synth.prefill_inputs(num_seqs=num_seqs, len_lo=len_lo, len_hi=len_hi)
+    bf = torch.bfloat16
     q, k, v = (p[x].to(bf).to(device) for x in "qkv")
     cu = p["cu_seqlens"].to(device)
-    fn = lambda: A.flash_attention_prefill(q, k, v, cu, p["scale"], 32, 8, 128)
-    ms = _time_calls([fn], 20, 5)
+    ms = _time_calls([lambda: A.flash_attention_prefill(q, k, v, cu, p["scale"], 32, 8, 128)], iters, 5)
     fl = synth.prefill_flops(p["lens"], 32, 128)
-    out["prefill_varlen_bf16"] = {"ms_per_call": ms, "TFLOPs": fl / ms / 1e9, "tokens": int(q.shape[0]),
-                                  "frac_of_measured_bf16_peak": fl / ms / 1e9 / pk["bf16_tflops"],
-                                  "frac_of_nominal_2250": fl / ms / 1e9 / 2250.0, "flops": fl,
-                                  "error_word": A.prefill_error_code(device)}
+    return {"ms_per_call": ms, "TFLOPs": fl / ms / 1e9, "tokens": int(q.shape[0]),
+            "frac_of_measured_bf16_peak": fl / ms / 1e9 / pk["bf16_tflops"],
+            "frac_of_nominal_2250": fl / ms / 1e9 / 2250.0, "flops": fl, "error_word": A.prefill_error_code(device)}
+
+
+def case_prefill_paged(device, pk, iters=10):
+    """Prefix-aware prefill: 16 sequences of [1024,2048] keys whose first half is already cached; the queries are
+    the uncached half, K/V are read through the block tables (32q/8kv, bf16, 256-token blocks)."""
+    from minivllm_b200.layers import attention as A
+    g = torch.Generator().manual_seed(6)
+    bf, H, KVH, D, bs = torch.bfloat16, 32, 8, 128, 256
+    klen = torch.randint(1024, 2049, (16,), generator=g)
+    qlen = klen // 2
+    nblk = (klen + bs - 1) // bs
+    total = int(nblk.sum())
+    perm = torch.randperm(total, generator=g).to(torch.int32)
+    bt = torch.full((16, int(nblk.max())), -1, dtype=torch.int32)
+    at = 0
+    for i, n in enumerate(nblk.tolist()):
+        bt[i, :n] = perm[at:at + n]
+        at += n
+    cu_q = torch.zeros(17, dtype=torch.int32)
+    cu_k = torch.zeros(17, dtype=torch.int32)
+    cu_q[1:], cu_k[1:] = torch.cumsum(qlen, 0), torch.cumsum(klen, 0)
+    gd = torch.Generator(device=device).manual_seed(6)
+    q = torch.randn(int(cu_q[-1]), H, D, generator=gd, device=device, dtype=torch.float32).to(bf)
+    kc = torch.randn(total, bs, KVH, D, generator=gd, device=device, dtype=torch.float32).to(bf)
+    vc = torch.randn(total, bs, KVH, D, generator=gd, device=device, dtype=torch.float32).to(bf)
+    args = (cu_q.to(device), cu_k.to(device), bt.to(device))
+    ms = _time_calls([lambda: A.flash_attention_prefill_paged(q, kc, vc, *args, 1.0 / D ** 0.5, H, KVH, D)], iters, 3)
+    fl = float(sum(4 * H * D * (int(ql) * (int(kl) - int(ql)) + int(ql) * (int(ql) + 1) // 2)
+                   for ql, kl in zip(qlen, klen)))
+    return {"ms_per_call": ms, "TFLOPs": fl / ms / 1e9, "query_tokens": int(cu_q[-1]), "key_tokens": int(cu_k[-1]),
+            "frac_of_measured_bf16_peak": fl / ms / 1e9 / pk["bf16_tflops"], "flops": fl,
+            "error_word": A.prefill_error_code(device)}
+
+
+def case_pre_attention(device, pk, iters=20):
+    """Fused q/k RMSNorm + RoPE + K/V store: 16,384 tokens, 32q/8kv heads of 128, bf16."""
+    from minivllm_b200.layers import attention as A
+    g = torch.Generator().manual_seed(5)
+    tokens, H, KVH, D = 16384, 32, 8, 128
+    bf = torch.bfloat16
+    qkv = torch.randn(tokens, (H + 2 * KVH) * D, generator=g).to(bf).to(device)
+    gam = torch.ones(D, dtype=bf, device=device)
+    pos = torch.randint(0, 2048, (tokens,), generator=g).to(device)
+    inv = 1.0 / (1e6 ** (torch.arange(0, D, 2).float() / D))
+    ang = torch.arange(2048).float()[:, None] * inv[None, :]
+    cos, sin = torch.cos(ang).to(device), torch.sin(ang).to(device)
+    kc = torch.zeros(128, 256, KVH, D, dtype=bf, device=device)
+    vc = torch.zeros_like(kc)
+    slots = torch.randperm(128 * 256, generator=g)[:tokens].to(device)
+    ms = _time_calls([lambda: A.qk_norm_rope_store(qkv, pos, cos, sin, gam, gam, 1e-5, H, KVH, D, kc, vc, slots)], iters, 3)
+    nbytes = tokens * ((H + 2 * KVH) * D * 2 + (H + KVH) * D * 2 + 2 * KVH * D * 2 + 16)
+    return _hbm(ms, nbytes, pk)
+
+
+def case_argmax(device, pk, iters=20):
+    """Greedy tail on decode-sized logits: 512 rows x 151,936 columns bf16."""
+    from minivllm_b200.layers import sampler as S
+    g = torch.Generator(device=device).manual_seed(5)
+    x = torch.randn(512, 151936, generator=g, device=device, dtype=torch.float32).to(torch.bfloat16)
+    ms = _time_calls([lambda: S.argmax_rows(x, want_keys=False, want_tokens=True)], iters, 3)
+    ref = _time_calls([lambda: x.argmax(dim=-1)], iters, 3)
+    same = bool((S.argmax_rows(x, want_keys=False, want_tokens=True)[1] == x.float().argmax(dim=-1)).all())
+    return _hbm(ms, x.numel() * 2 + 512 * 8, pk, torch_argmax_us=ref * 1e3, same_tokens_as_torch=same)
+
+
+def case_add_rmsnorm(device, pk, iters=20):
+    """Fused residual add + RMSNorm (single-rank form): 16,384 rows x 4096 bf16, residual updated in place."""
+    from minivllm_b200.layers.layernorm import add_rms_norm
+    g = torch.Generator(device=device).manual_seed(8)
+    x = torch.randn(16384, 4096, generator=g, device=device, dtype=torch.float32).to(torch.bfloat16)
+    res = [torch.zeros_like(x) for _ in range(2)]
+    gam = torch.ones(4096, dtype=torch.bfloat16, device=device)
+    out = torch.empty_like(x)
+    ms = _time_calls([lambda r=r: add_rms_norm(x, r, gam, 1e-5, residual_out=r, out=out) for r in res], iters, 3)
+    return _hbm(ms, x.numel() * 2 * 4, pk)
+
+
+def case_silu_mul(device, pk, iters=20):
+    """SwiGLU activation: 16,384 rows x (2 x 12,288) bf16 -> 16,384 x 12,288."""
+    from minivllm_b200.layers.activation import silu_and_mul
+    g = torch.Generator(device=device).manual_seed(9)
+    gu = torch.randn(16384, 2 * 12288, generator=g, device=device, dtype=torch.float32).to(torch.bfloat16)
+    ms = _time_calls([lambda: silu_and_mul(gu)], iters, 3)
+    return _hbm(ms, gu.numel() * 2 + gu.numel(), pk)
+
+
+OP_CASES = {
+    "decode_batch16_ctx64_1024": case_decode_cfg0,
+    "decode_tp8_shape_b512_4q1kv": case_decode_tp8_shape,
+    "decode_int8_b64_ctx1024_4096": case_decode_int8,
+    "store_kvcache_bf16": case_store,
+    "store_kvcache_int8": lambda device, pk, iters=50: case_store(device, pk, iters, int8=True),
+    "prefill_varlen_bf16": case_prefill,
+    "prefill_varlen_bf16_256seq_64_512": lambda device, pk, iters=20: case_prefill(device, pk, iters, 256, 64, 512),
+    "prefill_paged_bf16_16seq_half_cached": case_prefill_paged,
+    "qk_norm_rope_store_16384tok": case_pre_attention,
+    "argmax_rows_512x151936": case_argmax,
+    "add_rmsnorm_16384x4096": case_add_rmsnorm,
+    "silu_mul_16384x12288": case_silu_mul,
+}
+
+
+def extras(device, pk):
+    """Secondary numbers of the same run: every operator of the library at its benchmark shape."""
+    out = {}
+    for name, fn in OP_CASES.items():
+        out[name] = fn(device, pk)
+        torch.cuda.empty_cache()
     return out
 
+
+def run_ops(args, device, pk):
+    """One operator case, a handful of launches: the command the ncu summaries under profiles/ are made with."""
+    fn = OP_CASES[args.case]
+    res = fn(device, pk, iters=max(1, args.steps))
+    return {"metric": "operator case " + args.case, "value": res.get("us_per_call", res.get("ms_per_call")),
+            "unit": "us" if "us_per_call" in res else "ms", "n_gpus": 1, "steps": args.steps, "warmup": 3,
+            "higher_is_better": False, "data": "synthetic", "config": {"workload": (fn.__doc__ or args.case).strip()},
+            "extra": {args.case: res}}
 
 
 # ----------------------------------------------------------------------------
@@ -310,6 +482,7 @@ class EngineWorkload:
         out = e.generate(self.prompts, self.sp)
         assert sum(len(t) for t in out["token_ids"]) == self.out_tokens_per_step
         self.last_stats = dict(e.stats)
+        self.last_tokens = out["token_ids"]
         return out
 
     # host<->device traffic of one generate(): prompt ids + per-prefill-wave metadata, per decode step the slot
@@ -333,7 +506,9 @@ class EngineWorkload:
         decode_steps = self.out_tokens_per_step // len(self.prompts) - 1
         prefill_waves = s["steps"] - decode_steps
         tail = (2 if self.world > 1 else 1) if self.cfg.get("greedy", False) else 0
-        return decode_steps * (layers * 3 + 1 + tail) + prefill_waves * (layers * 2 + 2 + tail)
+        # per layer: fused q/k norm + RoPE + store, attention (decode: split-K + combine), two fused
+        # (all-reduce +) add + norm kernels, SwiGLU activation; per step: the first norm and the metadata kernel
+        return decode_steps * (layers * 6 + 2 + tail) + prefill_waves * (layers * 5 + 3 + tail)
 
     def decode_probe(self, iters=36):
         """Times paged_attention_decode with CUDA events on the engine's own KV pool at the shape of the
@@ -364,23 +539,59 @@ class EngineWorkload:
         nbytes = synth.decode_bytes(ctx, len(ctx), H, KVH, D, 2, r.max_blocks_per_seq)
         return dict(ms=ms, bytes=nbytes, gbps=nbytes / ms / 1e6, batch=len(ctx), ctx_mean=float(ctx.float().mean()))
 
+    def stream_check(self):
+        """Digest of the first 32 generated tokens of every request of the last step, and how many requests
+        produced exactly the tokens a TP=1 run of this benchmark produced (digests recorded in
+        tests/golden/engine_qwen3_8b_tp1_first32.json from a single-GPU run; absent file -> null count)."""
+        import hashlib
+        digs = [hashlib.blake2b(b"".join(int(t).to_bytes(4, "little") for t in toks[:32]), digest_size=8).hexdigest()
+                for toks in self.last_tokens]
+        all_d = hashlib.blake2b("".join(digs).encode(), digest_size=8).hexdigest()
+        out = {"requests": len(digs), "digest_of_first32": all_d, "identical_to_tp1_first32": None}
+        ref = os.path.join(ROOT, "tests", "golden", "engine_qwen3_8b_tp1_first32.json")
+        if os.path.exists(ref):
+            want = json.load(open(ref))["digests"]
+            if len(want) == len(digs):
+                out["identical_to_tp1_first32"] = sum(a == b for a, b in zip(digs, want))
+        dump = os.environ.get("MV_WRITE_FIRST32_DIGESTS")     # how the golden file is made (TP=1 run)
+        if dump and self.rank == 0:
+            json.dump({"workload": self.name, "tp": self.world, "digests": digs}, open(dump, "w"))
+        return out
+
     def close(self):
         self.engine.exit()
 
 
-def cpu_engine_reference(requests=1, prompt_len=512, new_tokens=2, log=None):
+CPU_SAMPLE = dict(requests=4, prompt_len=512, new_tokens=8)
+
+
+def cpu_engine_reference(requests=CPU_SAMPLE["requests"], prompt_len=CPU_SAMPLE["prompt_len"],
+                         new_tokens=CPU_SAMPLE["new_tokens"], repeats=1, warm=False):
     """The CPU path for the engine metric on a bounded sample: the same Qwen3-8B-shaped harness (same seeded
-    weights) with every attention operator replaced by the CPU oracle (fp32), fp32 activations, weights kept
-    in bf16 and up-cast layer by layer.  Returns (output tokens per second, seconds, description)."""
+    weights, plain torch formulation) with every attention operator replaced by the CPU oracle, fp32 weights and
+    activations (up-cast once, before the clock starts), all host cores, one batch of `requests` prompts of
+    `prompt_len` tokens prefilled together and decoded together for `new_tokens` greedy tokens each.
+    Both the `cpu_baseline` leg of the GPU run and `--impl reference` call this with the same sample.
+    Returns (output tokens per second, seconds per repeat, description)."""
     from minivllm_b200.engine import configs
     from minivllm_b200.engine.qwen3 import Qwen3Config, Qwen3ForCausalLM
     from minivllm_b200.utils.context import reset_context, set_context
     from oracle.attention_module import swap_in_oracle_attention
+    import psutil
+    cores = os.cpu_count() or 1
+    try:
+        cores = len(os.sched_getaffinity(0))
+    except (AttributeError, OSError):
+        pass
+    torch.set_num_threads(cores)      # torch.distributed.run exports OMP_NUM_THREADS=1; the CPU arm uses the host
     cfgd = configs.qwen3_8b_config(world_size=1)
     mc = Qwen3Config.from_dict(cfgd)
     build_dev = "cuda:0" if torch.cuda.is_available() else "cpu"   # weights are inputs: generate fast, then move
     model = Qwen3ForCausalLM(mc, 0, 1, torch.bfloat16, build_dev, seed=cfgd["seed"]).to("cpu")
     swap_in_oracle_attention(model)
+    fp32 = psutil.virtual_memory().available > 56e9
+    if fp32:
+        model.float()   # the reference model is fp32-only; 33 GB of weights, converted before timing
     bs = mc.block_size
     nblk = (prompt_len + new_tokens + bs - 1) // bs
     kv = torch.zeros(2, mc.num_layers, requests * nblk, bs, mc.num_kv_heads, mc.head_dim, dtype=torch.float32)
@@ -394,28 +605,33 @@ def cpu_engine_reference(requests=1, prompt_len=512, new_tokens=2, log=None):
         return torch.cat([tables[r, p // bs].long() * bs + p % bs
                           for r in range(requests) for p in [torch.arange(pos_lo, pos_hi)]])
 
+    def one_pass(new_tokens=new_tokens):
+        with torch.inference_mode():
+            cu = torch.arange(0, (requests + 1) * prompt_len, prompt_len, dtype=torch.int32)
+            set_context(True, cu, cu, prompt_len, prompt_len, slots(0, prompt_len), None, None,
+                        positions=torch.arange(prompt_len).repeat(requests),
+                        last_token_index=(cu[1:] - 1).long())
+            tok = model.compute_logits(model(ids.reshape(-1))).argmax(-1)
+            produced = requests
+            for t in range(1, new_tokens):
+                pos = prompt_len + t - 1
+                set_context(False, None, None, 0, 0, slots(pos, pos + 1), torch.full((requests,), pos + 1), tables,
+                            positions=torch.full((requests,), pos))
+                tok = model.compute_logits(model(tok)).argmax(-1)
+                produced += requests
+            reset_context()
+        return produced
+
+    if warm:
+        one_pass(2)                   # untimed: touches every weight once
     t0 = time.perf_counter()
-    with torch.inference_mode(), torch.autocast("cpu", enabled=False):
-        import psutil
-        if psutil.virtual_memory().available > 56e9:
-            model.float()  # fp32 math on the host (the reference model is fp32-only); 33 GB of weights
-        # else: bf16 weights stay as they are and torch's CPU bf16 GEMMs are used
-        cu = torch.arange(0, (requests + 1) * prompt_len, prompt_len, dtype=torch.int32)
-        set_context(True, cu, cu, prompt_len, prompt_len, slots(0, prompt_len), None, None,
-                    positions=torch.arange(prompt_len).repeat(requests),
-                    last_token_index=(cu[1:] - 1).long())
-        tok = model.compute_logits(model(ids.reshape(-1))).argmax(-1)
-        produced = requests
-        for t in range(1, new_tokens):
-            pos = prompt_len + t - 1
-            set_context(False, None, None, 0, 0, slots(pos, pos + 1), torch.full((requests,), pos + 1), tables,
-                        positions=torch.full((requests,), pos))
-            tok = model.compute_logits(model(tok)).argmax(-1)
-            produced += requests
-        reset_context()
-    dt = time.perf_counter() - t0
-    return produced / dt, dt, (f"{requests} request(s), prompt {prompt_len}, {new_tokens} greedy output tokens, fp32 on "
-                              f"{torch.get_num_threads()} host threads (weights up-cast from bf16 inside the timed region when host RAM allows)")
+    produced = sum(one_pass() for _ in range(repeats))
+    dt = (time.perf_counter() - t0) / repeats
+    desc = (f"{requests} requests prefilled and decoded as one batch, prompt {prompt_len} tokens each (the low end of "
+            f"the workload's [512,1536]), {new_tokens} greedy output tokens each, "
+            f"{'fp32' if fp32 else 'bf16 weights (host RAM too small for fp32)'} on {cores} host threads; weights "
+            f"built and converted before the clock starts")
+    return produced / repeats / dt, dt, desc
 
 def device_timed(fn, steps, warmup, dist_on):
     """W warm-up calls, then K calls each bracketed by CUDA events on the current stream; barrier and
@@ -451,30 +667,47 @@ def device_timed(fn, steps, warmup, dist_on):
 
 
 def finish(line, rank):
-    """Print the line and leave without NCCL / CUDA-graph teardown (destroying a process group whose
-    collectives live in captured graphs can block)."""
+    """Rank 0 prints the one JSON line."""
     if rank == 0:
         print(json.dumps(line), flush=True)
     sys.stdout.flush()
     sys.stderr.flush()
-    os._exit(0)
+
+
+def teardown(dist_on, limit_s=120.0):
+    """Normal shutdown: graphs and communicators are already closed by the workload; synchronise and destroy
+    the process group, then return so that the interpreter exits through its regular exit path (exit hooks
+    included).  A watchdog only guards against a teardown that blocks: after `limit_s` it runs the registered
+    exit hooks itself and leaves."""
+    def bail():
+        import atexit
+        sys.stderr.write("bench.py: teardown did not finish in %.0f s; running exit hooks and leaving\n" % limit_s)
+        sys.stderr.flush()
+        try:
+            atexit._run_exitfuncs()
+        finally:
+            os._exit(0)
+    timer = threading.Timer(limit_s, bail)
+    timer.daemon = True
+    timer.start()
+    torch.cuda.synchronize()
+    if dist_on:
+        import torch.distributed as dist
+        dist.barrier()
+        dist.destroy_process_group()
+    timer.cancel()
 
 
 def run_reference(args, rank):
     """CPU arm: rank 0 alone works; the other ranks exit 0."""
     if rank != 0:
         return
-    cores = torch.get_num_threads()
     if args.workload == "engine":
         metric, unit = "engine output tokens/s", "tok/s"
         name = EngineWorkload.name
-        vals, t_all, sample = [], 0.0, ""
-        for i in range(args.warmup + args.steps):
-            v, dt, sample = cpu_engine_reference()
-            if i >= args.warmup:
-                vals.append(v)
-                t_all += dt
-        value, ms = sum(vals) / len(vals), t_all / len(vals) * 1e3
+        # one model build, then an untimed pass and the timed passes of the same bounded sample
+        value, dt, sample = cpu_engine_reference(repeats=args.steps, warm=args.warmup > 0)
+        ms = dt * 1e3
         dtype, scaling = "f32", "strong"
     else:
         metric, unit = "paged-decode attention algorithmic HBM throughput", "GB/s"
@@ -493,7 +726,8 @@ def run_reference(args, rank):
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
             "scaling": scaling, "vs_baseline": None, "dtype": dtype, "data": "synthetic",
             "config": {"workload": name},
-            "cpu_baseline": {"value": value, "unit": unit, "cores": cores, "kind": "port", "sample": sample},
+            "cpu_baseline": {"value": value, "unit": unit, "cores": torch.get_num_threads(), "kind": "port",
+                             "sample": sample},
             "e2e": {"value": value, "unit": unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
     print(json.dumps(line), flush=True)
 
@@ -504,7 +738,8 @@ def main():
     ap.add_argument("--steps", type=int, default=None)
     ap.add_argument("--warmup", type=int, default=None)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="engine", choices=["engine", "decode"])
+    ap.add_argument("--workload", default="engine", choices=["engine", "decode", "allreduce", "ops"])
+    ap.add_argument("--case", default="store_kvcache_bf16", help="operator case of --workload ops: " + ", ".join(OP_CASES))
     ap.add_argument("--cpu-seconds", type=float, default=10.0)
     ap.add_argument("--no-extras", action="store_true", help="skip the secondary operator numbers and the CPU leg")
     ap.add_argument("--small", action="store_true",
@@ -518,7 +753,10 @@ def main():
         args.warmup = (3 if ours else 0) if args.warmup is None else args.warmup
         if not ours:
             args.steps = min(args.steps, 2)      # each CPU step is ~20-40 s of host work
-            args.warmup = min(args.warmup, 1)
+            args.warmup = min(args.warmup, 1)    # (a short pass that touches every weight once)
+    elif args.workload == "ops":
+        args.steps = 3 if args.steps is None else args.steps
+        args.warmup = 3
     else:
         args.steps = 50 if args.steps is None else args.steps
         args.warmup = 5 if args.warmup is None else args.warmup
@@ -544,54 +782,73 @@ def main():
     _cabi.lib()
     pk = peaks()
 
-    if args.workload == "engine" and args.small:
+    if args.workload == "engine":
+        line = run_engine(args, rank, world, local, device, dist_on, pk)
+    elif args.workload == "allreduce":
+        line = run_allreduce(args, rank, world, local, device, dist_on, pk)
+    elif args.workload == "ops":
+        line = run_ops(args, device, pk)
+    else:
+        line = run_decode(args, rank, world, local, device, dist_on, pk)
+    finish(line, rank)
+    teardown(dist_on)
+
+
+def run_engine(args, rank, world, local, device, dist_on, pk):
+    if args.small:
         # profiling case: same model and kernels, 32 requests x 8 tokens, eager decode (a launch list of a
-        # graph-capturing run would be dominated by the 36 captures)
+        # graph-capturing run would be dominated by the captures)
         wl = EngineWorkload(rank, world, device, requests=32, new_tokens=8, enforce_eager=True, num_kv_blocks=512)
         total_ms, call_ms, host_s = device_timed(wl.step, 1, 1, dist_on)
-        finish({"metric": "engine output tokens/s", "value": wl.units_per_step / (total_ms * 1e-3), "unit": "tok/s",
+        line = {"metric": "engine output tokens/s", "value": wl.units_per_step / (total_ms * 1e-3), "unit": "tok/s",
                 "n_gpus": world, "steps": 1, "warmup": 1, "config": {"workload": "profiling case: 32 requests x 8 "
-                "tokens of the engine workload, eager decode"}}, rank)
-    if args.workload == "engine":
-        wl = EngineWorkload(rank, world, device)
-        with ClockSampler(local, period_s=0.05) as clocks:
-            total_ms, call_ms, host_s = device_timed(wl.step, args.steps, args.warmup, dist_on)
-        value = wl.units_per_step * args.steps / (total_ms * 1e-3)
-        e2e_value = wl.units_per_step * args.steps / host_s
-        probe = wl.decode_probe()
-        s = wl.last_stats
-        line = {
-            "metric": "engine output tokens/s", "value": value, "unit": "tok/s", "n_gpus": world,
-            "steps": args.steps, "warmup": args.warmup, "ms_per_step": total_ms / args.steps,
-            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "config": {"workload": wl.name, "parallelism": f"tp{world}", "kv_blocks_per_gpu": wl.engine.model_runner.num_kv_blocks,
-                       "l2": "inputs larger than L2 (weights 16.4 GB and KV pool far exceed 126 MB)",
-                       "decode": "CUDA-graph replay of the whole step", "step": "one generate() over all requests"},
-            "e2e": {"value": e2e_value, "unit": "tok/s", "h2d_bytes_per_step": wl.h2d_bytes,
-                    "d2h_bytes_per_step": wl.d2h_bytes},
-            "gpu_launches": wl.launches_per_step() * args.steps,
-            "roofline": {"bound": "hbm", "achieved": probe["gbps"], "peak": pk["hbm_gbs"], "unit": "GB/s",
-                         "frac": probe["gbps"] / pk["hbm_gbs"], "traffic": probe["bytes"] * NCU_TRAFFIC_RATIO,
-                         "traffic_note": "ncu dram bytes of the batch-64 op case scaled by KV tokens",
-                         "peak_source": pk["src"], "kernel": "paged_decode_kernel (+combine)",
-                         "how": "CUDA events around the operator on the engine's KV pool, batch %d, mean ctx %.0f, "
-                                "one call per layer cache" % (probe["batch"], probe["ctx_mean"]),
-                         "ms_per_launch": probe["ms"], "frac_of_nominal_8TBs": probe["gbps"] / 8000.0},
-            "clocks": clocks.summary(),
-            "phase_split": {"prefill_s": s["prefill_s"], "decode_s": s["decode_s"], "engine_steps": s["steps"],
-                            "prefill_tokens": s["prefill_tokens"]},
-        }
-        if rank == 0 and world == 1 and not args.no_extras:
-            line["extra"] = extras(device, pk)
-            wl.close()
-            del wl
-            torch.cuda.empty_cache()
-            v, dt, sample = cpu_engine_reference()
-            line["cpu_baseline"] = {"value": v, "unit": "tok/s", "cores": torch.get_num_threads(), "kind": "port",
-                                    "sample": sample}
-        finish(line, rank)
+                "tokens of the engine workload, eager decode", "allreduce": wl.engine.model_runner.comm_note}}
+        wl.close()
+        return line
+    wl = EngineWorkload(rank, world, device)
+    with ClockSampler(local, period_s=0.05) as clocks:
+        total_ms, call_ms, host_s = device_timed(wl.step, args.steps, args.warmup, dist_on)
+    value = wl.units_per_step * args.steps / (total_ms * 1e-3)
+    e2e_value = wl.units_per_step * args.steps / host_s
+    probe = wl.decode_probe()
+    s = wl.last_stats
+    line = {
+        "metric": "engine output tokens/s", "value": value, "unit": "tok/s", "n_gpus": world,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": total_ms / args.steps,
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": wl.name, "parallelism": f"tp{world}", "kv_blocks_per_gpu": wl.engine.model_runner.num_kv_blocks,
+                   "l2": "inputs larger than L2 (weights 16.4 GB and KV pool far exceed 126 MB)",
+                   "decode": "CUDA-graph replay of the whole step, one step of lookahead on the host",
+                   "step": "one generate() over all requests", "allreduce": wl.engine.model_runner.comm_note},
+        "e2e": {"value": e2e_value, "unit": "tok/s", "h2d_bytes_per_step": wl.h2d_bytes,
+                "d2h_bytes_per_step": wl.d2h_bytes},
+        "gpu_launches": wl.launches_per_step() * args.steps,
+        "roofline": {"bound": "hbm", "achieved": probe["gbps"], "peak": pk["hbm_gbs"], "unit": "GB/s",
+                     "frac": probe["gbps"] / pk["hbm_gbs"], "traffic": probe["bytes"] * NCU_TRAFFIC_RATIO,
+                     "traffic_note": "ncu dram bytes of the batch-64 op case scaled by KV tokens",
+                     "peak_source": pk["src"], "kernel": "paged_decode_kernel (+combine)",
+                     "how": "CUDA events around the operator on the engine's KV pool, batch %d, mean ctx %.0f, "
+                            "one call per layer cache" % (probe["batch"], probe["ctx_mean"]),
+                     "ms_per_launch": probe["ms"], "frac_of_nominal_8TBs": probe["gbps"] / 8000.0},
+        "clocks": clocks.summary(),
+        "phase_split": {"prefill_s": s["prefill_s"], "decode_s": s["decode_s"], "engine_steps": s["steps"],
+                        "prefill_tokens": s["prefill_tokens"],
+                        "note": "host clock between launches; with a step in flight the split is approximate"},
+        "stream_check": wl.stream_check(),
+    }
+    wl.close()
+    if rank == 0 and world == 1 and not args.no_extras:
+        del wl
+        torch.cuda.empty_cache()
+        line["extra"] = extras(device, pk)
+        torch.cuda.empty_cache()
+        v, dt, sample = cpu_engine_reference()
+        line["cpu_baseline"] = {"value": v, "unit": "tok/s", "cores": torch.get_num_threads(), "kind": "port",
+                                "sample": sample}
+    return line
 
-    # ---- decode operator workload ----
+
+def run_decode(args, rank, world, local, device, dist_on, pk):
     if args.small:
         wl = DecodeWorkload(rank, device, batch=64, ctx_lo=1024, ctx_hi=4096)
         wl.name = wl.name.replace("batch 256, ctx uniform[1024,8192]", "batch 64, ctx uniform[1024,4096]")
@@ -625,7 +882,71 @@ def main():
         v, _ = time_cpu(run, nbytes / 1e9, min_seconds=args.cpu_seconds)
         line["cpu_baseline"] = {"value": v, "unit": "GB/s", "cores": torch.get_num_threads(), "kind": "port",
                                 "sample": sample}
-    finish(line, rank)
+    return line
+
+
+def run_allreduce(args, rank, world, local, device, dist_on, pk):
+    """The tensor-parallel step after o_proj / down_proj at the engine's two message sizes: decode (512 rows x
+    4096 bf16 = 4 MiB) and a prefill wave (16,384 rows = 128 MiB).  Times the fused all-reduce + residual +
+    RMSNorm kernel against what it replaces (NCCL all-reduce, then the residual add and RMSNorm on all rows),
+    CUDA events, max over ranks.  Link roofline: a rank moves (N-1)/N of the message in each direction."""
+    import torch.distributed as dist
+    import torch.nn.functional as F
+    from minivllm_b200.layers.allreduce import TPCommunicator, shard_rows
+    from minivllm_b200.layers.layernorm import add_rms_norm
+    assert world > 1, "--workload allreduce needs --gpus >= 2 (torch.distributed.run)"
+    hidden, dt = 4096, torch.bfloat16
+    comm = TPCommunicator(rank, world, 16384, hidden, dt, device)
+    gamma = torch.ones(hidden, dtype=dt, device=device)
+    out = {}
+    link_gbs = 770.0      # measured peer-copy bandwidth per direction on this pool (nominal 900)
+    for label, rows, iters in (("decode_512rows", 512, 400), ("prefill_16384rows", 16384, 40)):
+        g = torch.Generator(device=device).manual_seed(rank)
+        x = torch.randn(rows, hidden, generator=g, device=device, dtype=torch.float32).to(dt)
+        lo, hi = shard_rows(rows, rank, world)
+        shard = torch.zeros(max(hi - lo, 1), hidden, dtype=dt, device=device)
+        full_res = torch.zeros(rows, hidden, dtype=dt, device=device)
+        comm.input_rows(rows).copy_(x)
+
+        def fused():
+            comm.allreduce_residual_rmsnorm(rows, shard, gamma, 1e-5)
+
+        def nccl_fused_norm():       # NCCL + this library's local add+norm kernel on all rows
+            dist.all_reduce(x)
+            add_rms_norm(x, full_res, gamma, 1e-5, residual_out=full_res)
+
+        def nccl_torch():            # what the harness did before: NCCL, torch add, torch rms_norm
+            dist.all_reduce(x)
+            r = full_res + x
+            F.rms_norm(r, (hidden,), gamma, 1e-5)
+
+        res = {}
+        for name, fn in (("fused_kernel", fused), ("nccl_plus_add_norm_kernel", nccl_fused_norm),
+                         ("nccl_plus_torch_add_norm", nccl_torch)):
+            x.normal_()              # keep values finite across repeated in-place all-reduces
+            x.mul_(1e-3)
+            total_ms, _, _ = device_timed(lambda: [fn() for _ in range(iters)], 1, 3, dist_on)
+            res[name + "_us"] = total_ms * 1e3 / iters
+        torch.cuda.synchronize()
+        assert int(comm.error_word.item()) == 0, "an all-reduce wait ran out of time"
+        moved = rows * hidden * 2 * (world - 1) / world          # bytes per direction per rank
+        res["bytes_per_direction"] = moved
+        res["link_GBps_per_direction"] = moved / res["fused_kernel_us"] / 1e3
+        res["frac_of_measured_peer_copy_770GBps"] = res["link_GBps_per_direction"] / link_gbs
+        res["speedup_vs_nccl_torch"] = res["nccl_plus_torch_add_norm_us"] / res["fused_kernel_us"]
+        out[label] = res
+    d = out["decode_512rows"]
+    line = {"metric": "all-reduce + residual + RMSNorm latency (512 rows x 4096 bf16)", "value": d["fused_kernel_us"],
+            "unit": "us", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": d["fused_kernel_us"] / 1e3, "higher_is_better": False, "scaling": "strong",
+            "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": "tensor-parallel all-reduce + residual add + RMSNorm, hidden 4096 bf16, "
+                                   "512 rows (decode step) and 16,384 rows (prefill wave)",
+                       "l2": "the 4 MiB message is L2-resident by construction (the preceding GEMM just wrote it); "
+                             "the 128 MiB message exceeds L2"},
+            "gpu_launches": 2 * 3 * (400 + 40), "extra": out}
+    comm.close()
+    return line
 
 
 if __name__ == "__main__":

@@ -115,13 +115,15 @@ int mv_paged_decode(void* out, const void* q,
  * mv_paged_decode_static_capacity() bytes (8 MiB) inside the library's device
  * image, held by every GPU that loads the library.  Meant for a serving
  * process that gave all free HBM to the KV pool and forbids later
- * allocation, for code in callbacks or latency-critical loops where the
- * allocator must not run, and for bindings that only pass inputs and outputs.
+ * allocation, for latency-critical loops where the allocator must not run,
+ * and for bindings that only pass inputs and outputs (not for CUDA host
+ * callbacks: no launch may be made from one).
  * A problem needing more scratch than the array holds returns MV_ERR_LIMIT
  * and launches nothing.  All calls on a device share the array: calls that
  * overlap on the GPU race, so keep them on one stream or order them.  The
  * first call on each device resolves the array's address (a host-side lookup)
- * and should be made before any stream capture.  Neither function calls
+ * and should be made before any stream capture, from one host thread; the
+ * address is stale after a cudaDeviceReset.  Neither function calls
  * cudaMalloc, cudaFree or any allocating library routine.
  */
 int64_t mv_paged_decode_static_capacity(void);
@@ -297,7 +299,8 @@ int mv_argmax_decode(const int64_t* keys, int shards, int64_t rows,
  *   h[row] = round(residual * rsqrt(mean(residual^2) + eps) * gamma)
  * and h[row] is stored into the gather buffer of every rank.  The residual
  * stream stays sharded by rows: residual_shard is (owned rows, hidden).
- * Every rank must make the same sequence of calls with the same rows/hidden.
+ * Every rank must make the same sequence of calls with the same rows/hidden,
+ * one call at a time per communicator (calls are ordered by the stream).
  * Launch-only (graph-capturable); peers are read and written with plain loads
  * and stores.  A wait that runs out of time stores a non-zero code in
  * *error_word (caller-owned device int, zero-initialised; 0x100|peer = partial
@@ -309,9 +312,9 @@ int mv_argmax_decode(const int64_t* keys, int shards, int64_t rows,
  * mv_comm_create_emulated builds all N ranks on the current device; a call
  * then runs every rank in ONE cooperative launch (residual shard of rank p at
  * residual_shard + p*residual_slot_stride elements; mv_comm_input/output take
- * the rank as `slot`).  It exists to test the protocol on a single GPU and is
- * limited to 148 blocks in total.  On a real communicator `slot` is 0 and
- * residual_slot_stride is ignored.
+ * the rank as `slot`).  It exists to test the protocol on a single GPU (the
+ * launch uses at most one block per SM in total).  On a real communicator
+ * `slot` is 0 and residual_slot_stride is ignored.
  */
 int64_t mv_comm_handle_bytes(void);
 int mv_comm_create(int rank, int world, int64_t data_bytes, int timeout_ms,

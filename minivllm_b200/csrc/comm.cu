@@ -20,15 +20,20 @@
 // Plain peer loads and stores only: no TMA, no multicast, no library kernel
 // ever sees a peer pointer.
 //
-// Synchronisation: two flag barriers per launch (peers' partial sums complete
-// before they are read; every owner's rows landed before the kernel ends).
-// Block b of rank r pairs with block b of every peer, so every rank must
-// launch the same grid, which depends on (rows, world) only.  A flag is a
-// 32-bit generation number that its writer increases by one per launch; the
-// generation of a block lives in device memory and is advanced by the kernel
-// itself, so a captured graph replays correctly.  Every wait is bounded by a
-// timer (and an iteration cap): on expiry the block records a code in the
-// caller's error word and returns; later launches return at once while the
+// Synchronisation: two barriers per launch, one flag word per (rank, peer) each.
+//   ready: block 0 of a rank (dispatched first) tells every peer "my partial sums are
+//          complete" (their producer ran before this kernel in stream order); every
+//          block waits for all peers' ready flags before it reads their buffers.
+//   done:  a block that has stored its rows fences at system scope and counts itself
+//          on a local counter; the LAST block of the rank tells every peer "all my
+//          rows have landed" and alone waits for the peers' done flags, so the kernel
+//          ends only when this rank's gather buffer is complete.
+// A flag is a 32-bit generation number, one higher per launch; the generation lives in
+// device memory and is advanced by the kernel itself, so a captured graph replays
+// correctly.  No block waits for another block of its own GPU, and what a block waits
+// for on a peer is sent by the peer's first block, so the grid size is free.
+// Every wait is bounded by a timer (and an iteration cap): on expiry the block records a
+// code in the caller's error word and returns; later launches return at once while the
 // word is non-zero.  Nothing traps.
 //
 // A communicator can also be created in EMULATION mode: all N ranks' buffers
@@ -42,18 +47,24 @@
 namespace mv {
 
 constexpr int kMaxRanks = 8;
-constexpr int kMaxCommBlocks = 512;           // flag rows per phase
-constexpr int kCommGridCap = 2 * kNumSMs;     // resident blocks: every block of every rank must be co-scheduled
-constexpr size_t kCtrlBytes = 64 << 10;       // flags + generations + rank table, in front of the data buffers
+constexpr int kCommGridCap = 2 * kNumSMs;     // two 512-thread blocks per SM
+constexpr size_t kCtrlBytes = 64 << 10;       // flags + counters + rank table, in front of the data buffers
+
+// Barrier state at the start of every rank's region; every word sits in its own 128-byte line.
+struct CommCtrl {
+  uint32_t ready[kMaxRanks][32];   // ready[src][0]: written by rank src (remote store)
+  uint32_t done[kMaxRanks][32];    // done[src][0]:  written by rank src (remote store)
+  uint32_t gen[32];                // [0]: generation of the last completed launch (local)
+  uint32_t finished[32];           // [0]: blocks of this launch whose rows have landed (local)
+};
 
 // One entry per rank slot (one slot in a real communicator, N in emulation).
 struct CommSlot {
   const void* in[kMaxRanks];    // every rank's partial-sum buffer, indexed by rank
   void* out[kMaxRanks];         // every rank's gather buffer
-  uint32_t* flags[kMaxRanks];   // every rank's flag array [2][kMaxCommBlocks][kMaxRanks]
-  uint32_t* gen;                // this rank's per-block generation [kMaxCommBlocks]
+  CommCtrl* ctrl[kMaxRanks];    // every rank's barrier state
   int rank, world;
-  int skip_signal;              // test hook: withhold this slot's first-barrier signals once
+  int skip_signal;              // test hook: this slot withholds its ready signal
 };
 
 struct Comm {
@@ -69,9 +80,9 @@ struct Comm {
 };
 
 // Control region layout (byte offsets inside a rank's region).
-constexpr size_t kOffFlags = 0;                                                        // 2*512*8*4 = 32 KiB
-constexpr size_t kOffGen = kOffFlags + 2ull * kMaxCommBlocks * kMaxRanks * 4;          // 2 KiB
-constexpr size_t kOffTable = kOffGen + kMaxCommBlocks * 4;                             // 8 slots
+constexpr size_t kOffCtrl = 0;
+constexpr size_t kOffTable = 4096;
+static_assert(sizeof(CommCtrl) <= kOffTable, "barrier state overlaps the rank table");
 static_assert(kOffTable + kMaxRanks * sizeof(CommSlot) <= kCtrlBytes, "control region too small");
 
 static inline size_t round256(size_t x) { return (x + 255) & ~size_t(255); }
@@ -130,53 +141,73 @@ template <typename T> struct Vec8 {
   }
 };
 
-// Sum over the block of one float per thread; every thread gets the result.  `red` holds 33 floats.
-__device__ __forceinline__ float block_sum(float v, float* red) {
+// Sums over the block of R floats per thread; every thread gets the results.  `red` holds 33*R floats.
+template <int R>
+__device__ __forceinline__ void block_sum_n(float (&v)[R], float* red) {
 #pragma unroll
-  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  for (int r = 0; r < R; ++r)
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v[r] += __shfl_xor_sync(0xffffffffu, v[r], o);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = (blockDim.x + 31) >> 5;
-  __syncthreads();                       // `red` may still be read by the previous row
-  if (lane == 0) red[warp] = v;
+  __syncthreads();                       // `red` may still be read by the previous iteration
+  if (lane == 0)
+#pragma unroll
+    for (int r = 0; r < R; ++r) red[r * 33 + warp] = v[r];
   __syncthreads();
   if (warp == 0) {
-    float s = lane < nwarps ? red[lane] : 0.f;
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
-    if (lane == 0) red[32] = s;
+    for (int r = 0; r < R; ++r) {
+      float s = lane < nwarps ? red[r * 33 + lane] : 0.f;
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+      if (lane == 0) red[r * 33 + 32] = s;
+    }
   }
   __syncthreads();
-  return red[32];
+#pragma unroll
+  for (int r = 0; r < R; ++r) v[r] = red[r * 33 + 32];
+}
+__device__ __forceinline__ float block_sum(float v, float* red) {
+  float a[1] = {v};
+  block_sum_n<1>(a, red);
+  return a[0];
 }
 
 // ---------------------------------------------------------------------------------------------
 // all-reduce + residual + RMSNorm across ranks
 // ---------------------------------------------------------------------------------------------
-template <typename T, int VPT>
+// W = upper bound of the world size (sizes the register array of peer vectors), R = rows a block works
+// on at once (more loads in flight when few peers contribute per row), VPT = 16-byte vectors per thread
+// and row.
+template <typename T, int W, int R, int VPT>
 __global__ void __launch_bounds__(1024, 1)
 allreduce_residual_rmsnorm_kernel(CommSlot* __restrict__ table, void* __restrict__ residual_base,
                                   int64_t residual_slot_stride, const void* __restrict__ gamma_, float eps, int rows,
                                   int hidden, unsigned long long timeout_ns, int* __restrict__ error_word) {
-  __shared__ float red[33];
-  __shared__ int s_failed;
+  __shared__ float red[33 * R];
+  __shared__ int s_flag;
+  __shared__ uint32_t s_gen;
   CommSlot& slot = table[blockIdx.y];
-  const int rank = slot.rank, world = slot.world, blk = blockIdx.x, tid = threadIdx.x;
-  if (tid == 0) s_failed = *reinterpret_cast<volatile int*>(error_word) != 0;
+  const int rank = slot.rank, world = slot.world, tid = threadIdx.x;
+  CommCtrl* mine = slot.ctrl[rank];
+  if (tid == 0) {
+    s_flag = *reinterpret_cast<volatile int*>(error_word) != 0;
+    s_gen = *reinterpret_cast<volatile uint32_t*>(&mine->gen[0]) + 1;
+  }
   __syncthreads();
-  if (s_failed) return;                                             // an earlier wait ran out: do nothing
-  const uint32_t gen = slot.gen[blk] + 1;
-  uint32_t* my_flags = slot.flags[rank];
+  if (s_flag) return;                                               // an earlier wait ran out: do nothing
+  const uint32_t gen = s_gen;
 
-  // ---- barrier 1: every peer's partial sums are complete (their producer ran before this kernel in
-  // stream order; the release makes them visible to the peer that acquires the flag) ----
-  if (tid < world) {
-    if (!slot.skip_signal) st_release_sys(slot.flags[tid] + (0 * kMaxCommBlocks + blk) * kMaxRanks + rank, gen);
-    if (!wait_flag(my_flags + (0 * kMaxCommBlocks + blk) * kMaxRanks + tid, gen, timeout_ns)) {
+  // ---- ready: block 0 (dispatched first) signals the peers; every block waits for all peers ----
+  if (tid < world && tid != rank) {
+    if (blockIdx.x == 0 && !slot.skip_signal) st_release_sys(&slot.ctrl[tid]->ready[rank][0], gen);
+    if (!wait_flag(&mine->ready[tid][0], gen, timeout_ns)) {
       atomicCAS(error_word, 0, 0x100 | tid);
-      s_failed = 1;
+      s_flag = 1;
     }
   }
   __syncthreads();
-  if (s_failed) return;
+  if (s_flag) return;
 
   const int rows_per = (rows + world - 1) / world;
   const int lo = min(rows, rank * rows_per), hi = min(rows, lo + rows_per);
@@ -185,72 +216,102 @@ allreduce_residual_rmsnorm_kernel(CommSlot* __restrict__ table, void* __restrict
   const uint4* gamma = reinterpret_cast<const uint4*>(gamma_);
   const float inv_hidden = 1.0f / static_cast<float>(hidden);
 
-  for (int row = lo + blk; row < hi; row += gridDim.x) {
-    const size_t off = static_cast<size_t>(row) * nvec;
-    uint4 keep[VPT];
-    float ss = 0.f;
+  for (int row0 = lo + blockIdx.x * R; row0 < hi; row0 += gridDim.x * R) {
+    uint4 keep[R][VPT];
+    float ss[R];
+#pragma unroll
+    for (int r = 0; r < R; ++r) ss[r] = 0.f;
 #pragma unroll
     for (int v = 0; v < VPT; ++v) {
       const int c = tid + v * blockDim.x;
       if (c < nvec) {
-        uint4 part[kMaxRanks];
+        uint4 part[R][W];
 #pragma unroll
-        for (int p = 0; p < kMaxRanks; ++p)
-          if (p < world) part[p] = ld_global16(reinterpret_cast<const uint4*>(slot.in[p]) + off + c);
-        const uint4 res = reinterpret_cast<const uint4*>(residual)[static_cast<size_t>(row - lo) * nvec + c];
-        float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f}, f[8];
+        for (int r = 0; r < R; ++r)
+          if (row0 + r < hi) {
+            const size_t off = static_cast<size_t>(row0 + r) * nvec + c;
 #pragma unroll
-        for (int p = 0; p < kMaxRanks; ++p)
-          if (p < world) {
-            Vec8<T>::unpack(part[p], f);
+            for (int p = 0; p < W; ++p)
+              if (p < world) part[r][p] = ld_global16(reinterpret_cast<const uint4*>(slot.in[p]) + off);
+          }
+#pragma unroll
+        for (int r = 0; r < R; ++r)
+          if (row0 + r < hi) {
+            float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f}, f[8];
+#pragma unroll
+            for (int p = 0; p < W; ++p)
+              if (p < world) {
+                Vec8<T>::unpack(part[r][p], f);
+#pragma unroll
+                for (int i = 0; i < 8; ++i) acc[i] += f[i];
+              }
+            // round the all-reduced value to the model dtype, then the residual add in that dtype: the
+            // same roundings as `all_reduce(o); residual = residual + o`
+            const uint4 o = Vec8<T>::pack(acc);
+            Vec8<T>::unpack(o, acc);
+            Vec8<T>::unpack(reinterpret_cast<const uint4*>(residual)[static_cast<size_t>(row0 + r - lo) * nvec + c], f);
 #pragma unroll
             for (int i = 0; i < 8; ++i) acc[i] += f[i];
+            const uint4 rn = Vec8<T>::pack(acc);
+            reinterpret_cast<uint4*>(residual)[static_cast<size_t>(row0 + r - lo) * nvec + c] = rn;
+            keep[r][v] = rn;
+            Vec8<T>::unpack(rn, f);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) ss[r] += f[i] * f[i];
           }
-        // round the all-reduced value to the model dtype, then the residual add in that dtype: the
-        // same roundings as `all_reduce(o); residual = residual + o`
-        const uint4 o = Vec8<T>::pack(acc);
-        Vec8<T>::unpack(o, acc);
-        Vec8<T>::unpack(res, f);
-#pragma unroll
-        for (int i = 0; i < 8; ++i) acc[i] += f[i];
-        const uint4 rn = Vec8<T>::pack(acc);
-        reinterpret_cast<uint4*>(residual)[static_cast<size_t>(row - lo) * nvec + c] = rn;
-        keep[v] = rn;
-        Vec8<T>::unpack(rn, f);
-#pragma unroll
-        for (int i = 0; i < 8; ++i) ss += f[i] * f[i];
       }
     }
-    const float rstd = rsqrtf(block_sum(ss, red) * inv_hidden + eps);
+    block_sum_n<R>(ss, red);
 #pragma unroll
     for (int v = 0; v < VPT; ++v) {
       const int c = tid + v * blockDim.x;
       if (c < nvec) {
-        float gf[8], h[8];
+        float gf[8];
         Vec8<T>::unpack(gamma[c], gf);
-        Vec8<T>::unpack(keep[v], h);
 #pragma unroll
-        for (int i = 0; i < 8; ++i) h[i] = h[i] * rstd * gf[i];
-        const uint4 hv = Vec8<T>::pack(h);
+        for (int r = 0; r < R; ++r)
+          if (row0 + r < hi) {
+            const float rstd = rsqrtf(ss[r] * inv_hidden + eps);
+            float h[8];
+            Vec8<T>::unpack(keep[r][v], h);
 #pragma unroll
-        for (int p = 0; p < kMaxRanks; ++p)
-          if (p < world) {
-            const int dst = (rank + p) % world;           // spread the first stores over the links
-            st_global16(reinterpret_cast<uint4*>(slot.out[dst]) + off + c, hv);
+            for (int i = 0; i < 8; ++i) h[i] = h[i] * rstd * gf[i];
+            const uint4 hv = Vec8<T>::pack(h);
+            const size_t off = static_cast<size_t>(row0 + r) * nvec + c;
+#pragma unroll
+            for (int p = 0; p < W; ++p)
+              if (p < world) {
+                const int dst = rank + p < world ? rank + p : rank + p - world;   // spread the stores over the links
+                st_global16(reinterpret_cast<uint4*>(slot.out[dst]) + off, hv);
+              }
           }
       }
     }
   }
 
-  // ---- barrier 2: every owner's rows have landed in this rank's gather buffer ----
+  // ---- done: this block's rows have landed everywhere; the last block of the rank tells the peers and
+  // waits until every peer's rows have landed here ----
   __syncthreads();
-  if (tid < world) {
-    st_release_sys(slot.flags[tid] + (1 * kMaxCommBlocks + blk) * kMaxRanks + rank, gen);
-    if (!wait_flag(my_flags + (1 * kMaxCommBlocks + blk) * kMaxRanks + tid, gen, timeout_ns))
-      atomicCAS(error_word, 0, 0x200 | tid);
+  if (tid == 0) {
+    __threadfence_system();                      // this block's stores (ordered by the barrier) are performed
+    const bool last = atomicAdd(&mine->finished[0], 1u) == gridDim.x - 1;
+    if (last) {
+      __threadfence_system();                    // ... and so are those of every block counted before this one
+      for (int p = 0; p < world; ++p)
+        if (p != rank)
+          asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(&slot.ctrl[p]->done[rank][0]), "r"(gen) : "memory");
+    }
+    s_flag = last;
   }
   __syncthreads();
-  if (tid == 0) slot.gen[blk] = gen;
+  if (!s_flag) return;
+  if (tid < world && tid != rank)
+    if (!wait_flag(&mine->done[tid][0], gen, timeout_ns)) atomicCAS(error_word, 0, 0x200 | tid);
+  __syncthreads();
+  if (tid == 0) {          // ready for the next launch (ordered before it by the kernel boundary)
+    mine->finished[0] = 0;
+    mine->gen[0] = gen;
+  }
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -349,12 +410,19 @@ static int threads_for(int hidden, int* vpt) {
   return threads;
 }
 
-// Blocks per rank: one per owned row up to what is resident at once (two 512-thread blocks per SM, one
-// larger block), since paired blocks of different ranks wait on one another.  Depends on shapes only.
-static int comm_grid(int rows, int world, int threads) {
-  const int rows_per = (rows + world - 1) / world;
+// Rows a block works on at once: with few peers a row brings few remote bytes, so several rows keep the
+// links busy; only worth it when there are rows enough to occupy every resident block that way.
+static int comm_rows_at_once(int rows_per, int world, int vpt, int threads) {
+  if (vpt != 1) return 1;
   const int cap = threads <= 512 ? kCommGridCap : kNumSMs;
-  return rows_per < 1 ? 1 : (rows_per > cap ? cap : rows_per);
+  const int r = world <= 2 ? 4 : (world <= 4 ? 2 : 1);
+  return rows_per >= r * cap ? r : 1;
+}
+
+static int comm_grid(int rows_per, int at_once, int threads) {
+  const int cap = threads <= 512 ? kCommGridCap : kNumSMs;
+  const int want = (rows_per + at_once - 1) / at_once;
+  return want < 1 ? 1 : (want > cap ? cap : want);
 }
 
 static int cuda_fail(const char* what, cudaError_t e) {
@@ -370,9 +438,8 @@ static int write_table(Comm* c) {
     for (int p = 0; p < c->world; ++p) {
       t.in[p] = c->region[p] + kCtrlBytes;
       t.out[p] = c->region[p] + kCtrlBytes + round256(c->data_bytes);
-      t.flags[p] = reinterpret_cast<uint32_t*>(c->region[p] + kOffFlags);
+      t.ctrl[p] = reinterpret_cast<CommCtrl*>(c->region[p] + kOffCtrl);
     }
-    t.gen = reinterpret_cast<uint32_t*>(c->region[r] + kOffGen);
     t.rank = r;
     t.world = c->world;
     t.skip_signal = 0;
@@ -522,30 +589,55 @@ extern "C" int mv_debug_comm_withhold_signal(void* comm, int slot) {
   return e == cudaSuccess ? MV_OK : cuda_fail("comm: withhold", e);
 }
 
+template <typename T, int W, int R, int VPT>
+static int launch_allreduce_as(Comm* c, dim3 grid, int threads, void* residual, int64_t residual_slot_stride,
+                               const void* gamma, float eps, int rows, int hidden, int* error_word, cudaStream_t stream) {
+  CommSlot* table = c->table_dev;
+  unsigned long long timeout = c->timeout_ns;
+  if (!c->emulated) {
+    allreduce_residual_rmsnorm_kernel<T, W, R, VPT><<<grid, threads, 0, stream>>>(table, residual, residual_slot_stride,
+                                                                                  gamma, eps, rows, hidden, timeout, error_word);
+    return check_launch("allreduce_residual_rmsnorm");
+  }
+  // emulation: the blocks of all ranks wait on one another, so they must be co-resident
+  void* args[] = {&table, &residual, &residual_slot_stride, &gamma, &eps, &rows, &hidden, &timeout, &error_word};
+  const cudaError_t e = cudaLaunchCooperativeKernel(reinterpret_cast<const void*>(&allreduce_residual_rmsnorm_kernel<T, W, R, VPT>),
+                                                    grid, dim3(threads), args, 0, stream);
+  if (e != cudaSuccess) return cuda_fail("allreduce_residual_rmsnorm (emulated, cooperative launch)", e);
+  return MV_OK;
+}
+
 template <typename T>
 static int launch_allreduce(Comm* c, void* residual, int64_t residual_slot_stride, const void* gamma, float eps, int rows,
                             int hidden, int* error_word, cudaStream_t stream) {
   int vpt = 1;
   const int threads = threads_for(hidden, &vpt);
-  const dim3 grid(comm_grid(rows, c->world, threads), c->slots);
-  CommSlot* table = c->table_dev;
-  unsigned long long timeout = c->timeout_ns;
-  if (!c->emulated) {
-    if (vpt == 1)
-      allreduce_residual_rmsnorm_kernel<T, 1><<<grid, threads, 0, stream>>>(table, residual, residual_slot_stride, gamma, eps,
-                                                                            rows, hidden, timeout, error_word);
-    else
-      allreduce_residual_rmsnorm_kernel<T, 2><<<grid, threads, 0, stream>>>(table, residual, residual_slot_stride, gamma, eps,
-                                                                            rows, hidden, timeout, error_word);
-    return check_launch("allreduce_residual_rmsnorm");
+  const int rows_per = (rows + c->world - 1) / c->world;
+  int at_once = comm_rows_at_once(rows_per, c->world, vpt, threads);
+  int blocks = comm_grid(rows_per, at_once, threads);
+  if (c->emulated) {            // all ranks share one GPU: one row at a time, and few enough blocks to be co-resident
+    at_once = 1;
+    blocks = comm_grid(rows_per, 1, threads);
+    if (blocks * c->slots > kNumSMs) blocks = kNumSMs / c->slots;
   }
-  // emulation: the blocks of all ranks wait on one another, so they must be co-resident
-  void* args[] = {&table, &residual, &residual_slot_stride, &gamma, &eps, &rows, &hidden, &timeout, &error_word};
-  const void* fn = vpt == 1 ? reinterpret_cast<const void*>(&allreduce_residual_rmsnorm_kernel<T, 1>)
-                            : reinterpret_cast<const void*>(&allreduce_residual_rmsnorm_kernel<T, 2>);
-  const cudaError_t e = cudaLaunchCooperativeKernel(fn, grid, dim3(threads), args, 0, stream);
-  if (e != cudaSuccess) return cuda_fail("allreduce_residual_rmsnorm (emulated, cooperative launch)", e);
-  return MV_OK;
+  const dim3 grid(blocks, c->slots);
+#define MV_AR(W, R, V) \
+  return launch_allreduce_as<T, W, R, V>(c, grid, threads, residual, residual_slot_stride, gamma, eps, rows, hidden, error_word, stream)
+  if (vpt == 2) {
+    if (c->world <= 2) MV_AR(2, 1, 2);
+    if (c->world <= 4) MV_AR(4, 1, 2);
+    MV_AR(8, 1, 2);
+  }
+  if (c->world <= 2) {
+    if (at_once == 4) MV_AR(2, 4, 1);
+    MV_AR(2, 1, 1);
+  }
+  if (c->world <= 4) {
+    if (at_once == 2) MV_AR(4, 2, 1);
+    MV_AR(4, 1, 1);
+  }
+  MV_AR(8, 1, 1);
+#undef MV_AR
 }
 
 extern "C" int mv_allreduce_residual_rmsnorm(void* comm, void* residual_shard, int64_t residual_slot_stride,
@@ -566,9 +658,6 @@ extern "C" int mv_allreduce_residual_rmsnorm(void* comm, void* residual_shard, i
     const int rows_per = (rows + c->world - 1) / c->world;
     if (c->slots > 1 && residual_slot_stride < static_cast<int64_t>(rows_per) * hidden)
       return fail(MV_ERR_SHAPE, "allreduce_residual_rmsnorm: residual_slot_stride smaller than one rank's shard");
-    int vpt_unused = 1;
-    if (comm_grid(rows, c->world, threads_for(hidden, &vpt_unused)) * c->slots > kNumSMs)
-      return fail(MV_ERR_LIMIT, "allreduce_residual_rmsnorm: an emulated launch is limited to %d blocks in total", kNumSMs);
   }
   if (rows == 0) return MV_OK;
   cudaStream_t s = static_cast<cudaStream_t>(stream);

@@ -373,7 +373,7 @@ struct DecodeLayout {
 static DecodeLayout decode_layout(int batch, int num_heads, int num_kv_heads, int head_dim, int max_blocks,
                                   int block_size) {
   const int mtiles = (num_heads / num_kv_heads + 15) / 16;
-  const int64_t items = decode_items_max(batch, num_kv_heads, mtiles, max_blocks, block_size);
+  const int64_t items = decode_items_max(batch, num_kv_heads, mtiles);
   DecodeLayout L;
   L.binfo_off = 0;
   L.ml_off = ((static_cast<int64_t>(batch) * 8 + 255) / 256) * 256;

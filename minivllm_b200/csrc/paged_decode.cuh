@@ -12,7 +12,6 @@ constexpr int kDecThreads = kDecWarps * 32;
 constexpr int kDecStages = 3;
 constexpr int kTileTok = 16;                    // tokens per warp tile
 constexpr int kCtaTok = kTileTok * kDecWarps;   // tokens per CTA step
-constexpr int kChunkMax = 2048;                 // only sizes the scratch bound below (an older plan cut sequences at this length)
 constexpr int kDecCtasPerSM = 2;
 constexpr int kDecWaves = 1;                    // work units per resident CTA: units are equal in length, so one each
                                                 // is balanced; 2 and 4 measured slower (more pieces to merge)
@@ -46,12 +45,10 @@ __host__ __device__ inline int decode_target_items(int num_kv_heads, int mtiles)
   const int t = (kNumSMs * kDecCtasPerSM * kDecWaves) / (num_kv_heads * mtiles);
   return t < 1 ? 1 : t;
 }
-__host__ __device__ inline int64_t decode_items_max(int batch, int num_kv_heads, int mtiles, int max_blocks,
-                                                    int block_size) {
-  const int64_t lmax = static_cast<int64_t>(max_blocks) * block_size;
-  int64_t per_seq = (lmax + kChunkMax - 1) / kChunkMax;
-  if (per_seq < 1) per_seq = 1;
-  return decode_target_items(num_kv_heads, mtiles) + static_cast<int64_t>(batch) * per_seq;
+// Upper bound of the item ids: an item id is (sequence index + segment index) and there are at most
+// target_items segments, so ids stay below batch + target_items whatever the context lengths are.
+__host__ __device__ inline int64_t decode_items_max(int batch, int num_kv_heads, int mtiles) {
+  return static_cast<int64_t>(decode_target_items(num_kv_heads, mtiles)) + batch;
 }
 
 __device__ __forceinline__ int load_ctx(const DecodeParams& p, int b) {
@@ -216,7 +213,7 @@ __device__ __forceinline__ void merge_and_write(const DecodeParams& p, const flo
 template <typename T> int launch_decode_int8(const DecodeParams& p, cudaStream_t st);
 // Grid of the persistent decode kernels.
 inline int decode_grid(const DecodeParams& p) {
-  const int64_t items_max = decode_items_max(p.batch, p.num_kv_heads, p.mtiles, p.max_blocks, p.block_size);
+  const int64_t items_max = decode_items_max(p.batch, p.num_kv_heads, p.mtiles);
   int64_t grid = items_max * p.num_kv_heads * p.mtiles;
   const int64_t resident = static_cast<int64_t>(kNumSMs) * kDecCtasPerSM;
   return static_cast<int>(grid > resident ? resident : grid);

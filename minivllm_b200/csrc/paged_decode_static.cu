@@ -4,10 +4,11 @@
 // mv_paged_decode needs a scratch buffer for the partial results of sequences
 // whose KV range was split between CTAs, and its caller has to allocate that
 // buffer.  Some callers cannot: a serving process that handed all of its HBM
-// to the KV-cache pool at start-up and runs with allocation disabled, code
-// running where the allocator must not be touched (a host callback, a
-// latency-critical loop that may not take the allocator's lock), or a host
-// binding that was only ever given input and output pointers.  For them the scratch lives
+// to the KV-cache pool at start-up and runs with allocation disabled, a
+// latency-critical loop that may not take the allocator's lock, or a host
+// binding that was only ever given input and output pointers.  (It is not
+// for CUDA host callbacks: like any launch it may not be made from one.)
+// For them the scratch lives
 // in a fixed array in device memory that is part of this library: every GPU
 // that loads the library holds kStaticScratchBytes until the process exits.
 //
@@ -20,12 +21,15 @@
 //   * two calls that overlap on the GPU (different streams, or graphs
 //     replayed concurrently) race on the array.  Serialise them.
 //   * the first call on each device looks up the array's device address; make
-//     that first call outside any stream capture.
+//     that first call outside any stream capture, and from one host thread
+//     (the per-device table of addresses is filled without locking);
+//   * the looked-up address belongs to the device's current context: after a
+//     cudaDeviceReset it is stale and the library must be reloaded.
 #include "common.cuh"
 
 namespace mv {
 
-constexpr int64_t kStaticScratchBytes = 8ll << 20;  // 8 MiB: batch 256 at 16 query heads, or batch 1024 at 4
+constexpr int64_t kStaticScratchBytes = 8ll << 20;  // 8 MiB: e.g. batch 440 at 32 query heads, batch 950 at 16 (any context length)
 
 // In host code this name is only a handle for the runtime, not an address a
 // kernel could use: the device address comes from cudaGetSymbolAddress below.

@@ -12,7 +12,10 @@ reference's outputs are stored, as fp32):
                      `paged_attention_decode` under TRITON_INTERPRET=1;
   * prefill_*.npz  : benchmark_prefilling.py `pytorch_standard_attention` and
                      the Triton kernel `flash_attention_prefill` (interpreter);
-  * store_*.npz    : the Triton kernel `store_kvcache` (interpreter).
+  * store_*.npz    : the Triton kernel `store_kvcache` (interpreter);
+  * layers_small.npz : the reference's LayerNorm (residual add + RMSNorm) and SiluAndMul modules;
+  * model_logits.npz : the reference's whole Qwen3ForCausalLM (models/qwen3.py), fp32, toy size, with the
+                     harness model's seeded weights copied in: logits of one prefill and one decode step.
 The fixtures are small so that the interpreter finishes in seconds and the
 files stay a few hundred KB.
 """
@@ -27,7 +30,9 @@ import torch
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 ROOT = os.path.dirname(os.path.dirname(HERE))
-REF = os.environ.get("MINIVLLM_REFERENCE", os.path.join(os.sep, "root", "reference"))
+REF = os.environ.get("MINIVLLM_REFERENCE")
+if not REF or not os.path.isdir(REF):
+    sys.exit("set MINIVLLM_REFERENCE to a checkout of the reference engine")
 sys.path.insert(0, ROOT)
 sys.path.insert(0, REF)
 sys.path.insert(0, os.path.join(REF, "src"))
@@ -175,12 +180,94 @@ def prenorm_main():
     print("prenorm_rope", qo.shape, ko.shape)
 
 
+def layers_main():
+    """Residual add + RMSNorm and the SwiGLU activation through the reference's own modules (fp32, CPU):
+    LayerNorm.forward(x, residual) (src/myvllm/layers/layernorm.py:24-28) and SiluAndMul
+    (src/myvllm/layers/activation.py:17-20)."""
+    from myvllm.layers.activation import SiluAndMul
+    from myvllm.layers.layernorm import LayerNorm
+    g = torch.Generator().manual_seed(50)
+    x = torch.randn(11, 96, generator=g)
+    residual = torch.randn(11, 96, generator=g) * 2
+    gamma = torch.rand(96, generator=g) + 0.5
+    normed, new_res = LayerNorm(gamma)(x, residual)
+    plain = LayerNorm(gamma)(x)
+    gu = torch.randn(7, 2 * 40, generator=g) * 2
+    act = SiluAndMul()(gu)
+    np.savez_compressed(os.path.join(HERE, "layers_small.npz"), seed=50, normed=normed.numpy(),
+                        new_residual=new_res.numpy(), plain=plain.numpy(), act=act.numpy())
+    print("layers_small", normed.shape, act.shape)
+
+
+MODEL_CASE = dict(vocab_size=211, hidden_size=256, num_layers=2, num_heads=4, num_kv_heads=2, head_dim=64,
+                  intermediate_size=96, max_position=64, block_size=16, seed=3, lens=(5, 9))
+
+
+def model_main():
+    """Logits of the reference's own Qwen3ForCausalLM (src/myvllm/models/qwen3.py:276-331) on the CPU in fp32:
+    one prefill step over two sequences and one decode step, attention through the reference's Triton kernels
+    (interpreter).  The weights are the harness model's seeded weights copied in; the only shims are the ones
+    the reference cannot run without: a one-rank gloo group (its layers query the process group), biases off,
+    `Attention.block_size` set to the cache's block size, and the context set by hand as its model runner
+    would (src/myvllm/engine/model_runner.py:217-226,246-255)."""
+    import torch.distributed as dist
+    if not dist.is_initialized():
+        dist.init_process_group("gloo", init_method="tcp://127.0.0.1:29779", world_size=1, rank=0)
+    from myvllm.models.qwen3 import Qwen3ForCausalLM as RefModel
+    from myvllm.utils import reset_context, set_context
+    from minivllm_b200.engine.qwen3 import Qwen3Config, Qwen3ForCausalLM
+    c = MODEL_CASE
+    cfg = Qwen3Config(vocab_size=c["vocab_size"], hidden_size=c["hidden_size"], num_layers=c["num_layers"],
+                      num_heads=c["num_heads"], num_kv_heads=c["num_kv_heads"], head_dim=c["head_dim"],
+                      intermediate_size=c["intermediate_size"], max_position=c["max_position"],
+                      block_size=c["block_size"], tie_word_embeddings=True)
+    ours = Qwen3ForCausalLM(cfg, 0, 1, torch.float32, "cpu", seed=c["seed"])
+    ref = RefModel(vocab_size=c["vocab_size"], hidden_size=c["hidden_size"], num_heads=c["num_heads"],
+                   head_dim=c["head_dim"], num_kv_heads=c["num_kv_heads"], intermediate_size=c["intermediate_size"],
+                   num_layers=c["num_layers"], base=1000000, max_position=c["max_position"], ffn_bias=False,
+                   qkv_bias=False, tie_word_embeddings=True)
+    with torch.no_grad():
+        ref.qwen3_model.embedding_layer.weight.copy_(ours.embed)
+        for mine, theirs in zip(ours.layers, ref.qwen3_model.layer_stack):
+            theirs.self_attn.qkv_projection.weight.copy_(mine.qkv_w)
+            theirs.self_attn.output_projection.weight.copy_(mine.o_w)
+            theirs.mlp.gate_up.weight.copy_(mine.gate_up_w)
+            theirs.mlp.gate_down.weight.copy_(mine.down_w)
+    bs, lens = c["block_size"], c["lens"]
+    kv = torch.zeros(2, c["num_layers"], 4, bs, c["num_kv_heads"], c["head_dim"])
+    for l, layer in enumerate(ref.qwen3_model.layer_stack):
+        a = layer.self_attn.attention
+        a.k_cache, a.v_cache, a.block_size = kv[0, l], kv[1, l], bs
+    g = torch.Generator().manual_seed(c["seed"])
+    ids = torch.randint(0, c["vocab_size"], (sum(lens),), generator=g)
+    cu = torch.tensor([0, lens[0], lens[0] + lens[1]], dtype=torch.int32)
+    tables = torch.tensor([[2], [0]], dtype=torch.int32)             # one 16-token block per sequence
+    slot_prefill = torch.cat([tables[i, 0].long() * bs + torch.arange(n) for i, n in enumerate(lens)])
+    with torch.inference_mode():
+        set_context(True, cu, cu, max(lens), max(lens), slot_prefill, None, None)
+        prefill_logits = ref.compute_logits(ref(ids)).clone()
+        tok = prefill_logits.argmax(-1)
+        ctx_lens = torch.tensor([n + 1 for n in lens], dtype=torch.int32)
+        slot_decode = torch.tensor([int(tables[i, 0]) * bs + n for i, n in enumerate(lens)], dtype=torch.int64)
+        set_context(False, None, None, 0, 0, slot_decode, ctx_lens, tables)
+        decode_logits = ref.compute_logits(ref(tok)).clone()
+        reset_context()
+    np.savez_compressed(os.path.join(HERE, "model_logits.npz"), case=repr(c), input_ids=ids.numpy(),
+                        prefill_logits=prefill_logits.numpy(), decode_input=tok.numpy(),
+                        decode_logits=decode_logits.numpy())
+    print("model_logits", prefill_logits.shape, decode_logits.shape, tok.tolist())
+
+
 if __name__ == "__main__":
     only = [a for a in sys.argv[1:] if a.startswith("--only=")]
-    which = only[0].split("=")[1].split(",") if only else ["ops", "metadata", "prenorm"]
+    which = only[0].split("=")[1].split(",") if only else ["ops", "metadata", "prenorm", "layers", "model"]
     if "ops" in which:
         main()
     if "metadata" in which:
         metadata_main()
     if "prenorm" in which:
         prenorm_main()
+    if "layers" in which:
+        layers_main()
+    if "model" in which:
+        model_main()

@@ -1,0 +1,32 @@
+"""The fused all-reduce + residual + RMSNorm kernel on real peer memory: one process per GPU (needs >= 2 GPUs;
+skipped otherwise -- the single-GPU suite covers the same kernel through the emulated communicator)."""
+import os
+import subprocess
+import sys
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs at least 2 GPUs")
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_allreduce_across_gpus(world):
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
+    env = dict(os.environ, MASTER_ADDR="127.0.0.1", MASTER_PORT=str(29620 + world), WORLD_SIZE=str(world),
+               NCCL_NVLS_ENABLE="0")
+    procs = [subprocess.Popen([sys.executable, os.path.join(ROOT, "tests", "tp_allreduce_worker.py")],
+                              env=dict(env, RANK=str(r)), stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
+             for r in range(world)]
+    outs = []
+    for p in procs:
+        try:
+            outs.append(p.communicate(timeout=240)[0])
+        except subprocess.TimeoutExpired:
+            p.kill()
+            outs.append(p.communicate()[0] + "\n[timed out]")
+    assert all(p.returncode == 0 for p in procs), "\n".join(o[-2000:] for o in outs)
+    assert all(f"TP_ALLREDUCE_OK {r}" in outs[r] for r in range(world))

@@ -5,7 +5,6 @@ is sized with, units are equal in length, and the walk of a CTA visits exactly t
 import random
 
 K_CTA_TOK = 64          # kTileTok * kDecWarps
-K_CHUNK_MAX = 2048
 NUM_SMS, CTAS_PER_SM, WAVES = 148, 2, 1
 
 
@@ -13,9 +12,8 @@ def target_items(num_kv_heads, mtiles):
     return max((NUM_SMS * CTAS_PER_SM * WAVES) // (num_kv_heads * mtiles), 1)
 
 
-def items_max(batch, num_kv_heads, mtiles, max_blocks, block_size):
-    per_seq = max((max_blocks * block_size + K_CHUNK_MAX - 1) // K_CHUNK_MAX, 1)
-    return target_items(num_kv_heads, mtiles) + batch * per_seq
+def items_max(batch, num_kv_heads, mtiles):
+    return target_items(num_kv_heads, mtiles) + batch
 
 
 def build_plan(ctx, target):
@@ -84,7 +82,7 @@ def _check(ctx, num_kv_heads, mtiles, grid):
             assert p["tok_end"] - p["tok_begin"] <= seg_len
             first, count = seq_items(s_tok, seg_len, p["b"])
             assert count == p["nsplit"] and first <= p["item"] < first + count
-            assert p["item"] < items_max(batch, num_kv_heads, mtiles, (max(ctx) + 15) // 16 or 1, 16)
+            assert p["item"] < items_max(batch, num_kv_heads, mtiles)
             assert p["item"] not in ids.setdefault(y, set())
             ids[y].add(p["item"])
             covered.setdefault((y, p["b"]), []).append((p["tok_begin"], p["tok_end"]))

@@ -88,11 +88,9 @@ def _emulated_case(comm, rows, hidden, dtype, seed):
 def test_emulated_allreduce_residual_rmsnorm(world, dtype):
     """Several calls in a row on one communicator (the generation counters advance), with row counts that
     divide evenly, leave a ragged tail, and leave some ranks without rows."""
-    comm = EmulatedCommunicator(world, 64, 4096, dtype, DEV)
+    comm = EmulatedCommunicator(world, 640, 4096, dtype, DEV)
     try:
-        for i, rows in enumerate([world * 4, 64, 5, 1, world + 1, 64]):
-            if (rows + world - 1) // world * world > 148:
-                continue
+        for i, rows in enumerate([world * 4, 64, 5, 1, world + 1, 64, 640]):
             _emulated_case(comm, rows, 4096, dtype, seed=100 * world + i)
     finally:
         comm.close()
