@@ -298,7 +298,8 @@ int mv_argmax_decode(const int64_t* keys, int shards, int64_t rows,
  *   residual_shard[row - first owned row] = round(residual_shard[...] + o);
  *   h[row] = round(residual * rsqrt(mean(residual^2) + eps) * gamma)
  * and h[row] is stored into the gather buffer of every rank.  The residual
- * stream stays sharded by rows: residual_shard is (owned rows, hidden).
+ * stream stays sharded by rows: residual_shard is (owned rows, hidden) and may
+ * be null on a rank that owns no row (rows < world).
  * Every rank must make the same sequence of calls with the same rows/hidden,
  * one call at a time per communicator (calls are ordered by the stream).
  * Launch-only (graph-capturable); peers are read and written with plain loads

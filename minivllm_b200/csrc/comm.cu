@@ -644,8 +644,13 @@ extern "C" int mv_allreduce_residual_rmsnorm(void* comm, void* residual_shard, i
                                              const void* gamma, float eps, int rows, int hidden, int* error_word,
                                              int dtype, void* stream) {
   Comm* c = static_cast<Comm*>(comm);
-  if (!c || !residual_shard || !gamma || !error_word) return fail(MV_ERR_NULL, "allreduce_residual_rmsnorm: null argument");
+  if (!c || !gamma || !error_word) return fail(MV_ERR_NULL, "allreduce_residual_rmsnorm: null argument");
   if (!c->connected) return fail(MV_ERR_SHAPE, "allreduce_residual_rmsnorm: communicator is not connected");
+  if (!residual_shard) {      // allowed only for a rank that owns no row of this call
+    const int per = rows > 0 ? (rows + c->world - 1) / c->world : 0;
+    if (c->emulated || static_cast<int64_t>(c->rank) * per < rows)
+      return fail(MV_ERR_NULL, "allreduce_residual_rmsnorm: residual_shard is null but this rank owns rows");
+  }
   if (rows < 0 || hidden <= 0 || hidden % 8 != 0)
     return fail(MV_ERR_SHAPE, "allreduce_residual_rmsnorm: hidden (%d) must be a positive multiple of 8, rows >= 0", hidden);
   if (hidden > 16384) return fail(MV_ERR_LIMIT, "allreduce_residual_rmsnorm: hidden %d exceeds 16384", hidden);

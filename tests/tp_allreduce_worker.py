@@ -34,9 +34,7 @@ def main():
         residual = (torch.randn(rows, hidden, generator=g) * 2).to(dtype)
         gamma = (1 + 0.1 * torch.randn(hidden, generator=g)).to(dtype)
         lo, hi = shard_rows(rows, rank, world)
-        shard = residual[lo:hi].to(dev).contiguous()
-        if shard.numel() == 0:
-            shard = torch.zeros(1, hidden, dtype=dtype, device=dev)
+        shard = residual[lo:hi].to(dev).contiguous()       # empty (null pointer) on a rank without rows
         comm.input_rows(rows).copy_(partials[rank])
         out = comm.allreduce_residual_rmsnorm(rows, shard, gamma.to(dev), EPS)
         torch.cuda.synchronize()
