@@ -468,6 +468,8 @@ class EngineWorkload:
         from minivllm_b200.engine import configs
         from minivllm_b200.engine.llm_engine import LLMEngine
         self.rank, self.world, self.device = rank, world, device
+        if os.environ.get("MV_CUSTOM_ALLREDUCE", "1") == "0":      # A/B switch: the NCCL all-reduce path
+            cfg_over.setdefault("custom_allreduce", False)
         self.cfg = configs.qwen3_8b_config(world_size=world, **cfg_over)
         self.prompts, self.sp = configs.qwen3_8b_requests(n=requests, new_tokens=new_tokens)
         self.engine = LLMEngine(self.cfg, rank=rank, world_size=world)

@@ -274,6 +274,29 @@ int mv_argmax_decode(const int64_t* keys, int shards, int64_t rows,
                      int64_t* tokens, void* stream);
 
 /*
+ * Temperature sampling tail, vocabulary-sharded.  Replaces the sampler
+ * src/myvllm/layers/sampler.py:15-19 (logits / T, softmax, division by an
+ * Exp(1) draw per entry, argmax) and the logits gather in front of it
+ * (layers/embedding_head.py:56-77):  argmax_i p_i / E_i equals
+ * argmax_i (logit_i / T - log E_i), which needs no softmax normaliser, so
+ * every rank reduces its shard to the same 64-bit keys as mv_argmax_rows
+ * (score in place of the logit) and the shards merge by integer MAX
+ * (mv_argmax_decode).  E_i comes from Philox4x32-10 with key = seed and
+ * counter = (global column / 4, row, *step): every rank and every
+ * tensor-parallel degree draws the same noise for a given global column.
+ * temperatures is (rows) fp32; a row with temperature 0 is greedy.  *step is
+ * read on the device (a captured graph can advance it between replays).
+ * mv_philox4x32_10 evaluates the generator on the host (for checking).
+ */
+int mv_sample_rows(const void* logits, int64_t row_stride, int64_t rows,
+                   int64_t cols, int64_t index_offset,
+                   const float* temperatures, uint64_t seed,
+                   const int64_t* step, int64_t* keys, int64_t* tokens,
+                   int dtype, void* stream);
+int mv_philox4x32_10(uint64_t seed, uint64_t step, uint32_t row,
+                     uint32_t column_group, uint32_t* out4);
+
+/*
  * Tensor-parallel all-reduce over NVLink peer memory, fused with the residual
  * add and the RMSNorm that follow it.
  * Replaces: the `dist.all_reduce(result)` that ends every row-parallel linear

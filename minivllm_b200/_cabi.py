@@ -48,6 +48,9 @@ SIGNATURES = {
                                        _c_int, _c_int, _c_ptr]),
     "mv_argmax_rows": (_c_int, [_c_ptr, _c_i64, _c_i64, _c_i64, _c_i64, _c_ptr, _c_ptr, _c_int, _c_ptr]),
     "mv_argmax_decode": (_c_int, [_c_ptr, _c_int, _c_i64, _c_ptr, _c_ptr]),
+    "mv_sample_rows": (_c_int, [_c_ptr, _c_i64, _c_i64, _c_i64, _c_i64, _c_ptr, ctypes.c_uint64, _c_ptr, _c_ptr, _c_ptr,
+                                _c_int, _c_ptr]),
+    "mv_philox4x32_10": (_c_int, [ctypes.c_uint64, ctypes.c_uint64, ctypes.c_uint32, ctypes.c_uint32, _c_ptr]),
     "mv_comm_handle_bytes": (_c_i64, []),
     "mv_comm_create": (_c_int, [_c_int, _c_int, _c_i64, _c_int, ctypes.POINTER(_c_ptr), _c_ptr]),
     "mv_comm_connect": (_c_int, [_c_ptr, _c_ptr]),

@@ -32,6 +32,9 @@ class LLMEngine:
         seq = Sequence(token_ids, sampling_params, block_size=self.block_size)
         if len(seq) + seq.max_tokens > self.model_runner.max_model_len:
             raise ValueError("prompt + max_tokens exceeds max_model_length")
+        if self.model_runner.greedy and seq.temperature != 0:
+            raise ValueError("this engine was configured with greedy=True (argmax for every request); "
+                             "use temperature 0, or greedy=False for per-request temperatures")
         self.scheduler.add_sequence(seq)
         return seq
 

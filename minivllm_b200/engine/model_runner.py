@@ -24,7 +24,7 @@ import torch.distributed as dist
 from ..layers.attention import _error_word
 from ..utils.context import get_context, reset_context, set_context
 from .metadata import SequenceStateTable
-from ..layers.sampler import greedy_tokens
+from ..layers.sampler import greedy_tokens, sampled_tokens
 from .qwen3 import Qwen3Config, Qwen3ForCausalLM
 
 
@@ -63,8 +63,10 @@ class ModelRunner:
         self.num_slots = self.max_num_seqs + 1
         self.pad_slot = self.max_num_seqs
         self.state = SequenceStateTable(self.num_slots, self.max_blocks_per_seq, self.block_size, self.device)
-        # the default CUDA generator is the one CUDA graphs know how to replay; same seed on every TP rank
-        torch.cuda.manual_seed(config.get("sample_seed", 1234))
+        # temperature sampling: same seed on every rank, a step counter in device memory that the decode graph
+        # advances itself
+        self.sample_seed = int(config.get("sample_seed", 1234))
+        self.sample_step = torch.zeros(1, dtype=torch.int64, device=self.device)
         self.graphs, self.graph_vars = {}, None
         self.decode_workspace = None
         self._stage, self._stage_at, self._stage_dev = None, 0, None
@@ -208,24 +210,26 @@ class ModelRunner:
                     positions=bufs["positions"], decode_workspace=self.decode_workspace)
 
     # ---------------------------------------------------------------- sampling ---
-    def sample(self, logits, temperatures=None):
-        """The reference's exponential-race draw (src/myvllm/layers/sampler.py:15-19) on full-vocabulary logits."""
-        probs = torch.softmax(logits.float() / temperatures.unsqueeze(-1), dim=-1)
-        noise = torch.empty_like(probs).exponential_(1).clamp_min_(1e-10)
-        return probs.div_(noise).argmax(dim=-1)
-
     def next_tokens(self, hidden, temperatures=None):
-        """hidden states -> sampled token ids.  Greedy: each rank multiplies by its slice of the vocabulary only
-        and the ranks merge one 64-bit key per row (layers/sampler.py) instead of gathering or replicating the
-        151,936-wide logits; with a temperature every rank computes the full logits and draws with the same seed."""
+        """hidden states -> sampled token ids.  Each rank multiplies by its slice of the vocabulary only and
+        reduces it to one 64-bit key per row (layers/sampler.py): the row maximum when greedy, the best
+        exponential-race score (the reference's sampler, src/myvllm/layers/sampler.py:15-19, without its softmax)
+        when sampling with temperatures -- rows with temperature 0 are greedy.  Ranks merge the keys by MAX
+        instead of gathering or replicating the 151,936-wide logits, and end with identical tokens: the race's
+        noise depends on (seed, step, row, global column) only."""
+        vocab = self.model.lm_head.shape[0]
+        shard = self.world_size > 1 and vocab % self.world_size == 0
+        if shard:
+            logits = self.model.compute_logits(hidden, (self.rank, self.world_size))
+            offset, world = self.rank * (vocab // self.world_size), self.world_size
+        else:
+            logits = self.model.compute_logits(hidden)
+            offset, world = 0, 1
         if self.greedy or temperatures is None:
-            vocab = self.model.lm_head.shape[0]
-            shard = self.world_size > 1 and vocab % self.world_size == 0
-            if shard:
-                logits = self.model.compute_logits(hidden, (self.rank, self.world_size))
-                return greedy_tokens(logits, self.rank * (vocab // self.world_size), None, self.world_size)
-            return greedy_tokens(self.model.compute_logits(hidden))
-        return self.sample(self.model.compute_logits(hidden), temperatures)
+            return greedy_tokens(logits, offset, None, world)
+        tokens = sampled_tokens(logits, temperatures, self.sample_seed, self.sample_step, offset, None, world)
+        self.sample_step.add_(1)
+        return tokens
 
     # --------------------------------------------------------------------- run ---
     @torch.inference_mode()

@@ -134,16 +134,7 @@ class DecoderLayer(nn.Module):
         else:
             residual = residual + x
             h = F.rms_norm(residual, (residual.shape[-1],), self.input_norm_w, RMS_EPS)
-        qkv = F.linear(h, self.qkv_w)
-        v = qkv[:, (self.h + self.kvh) * self.d:].view(-1, self.kvh, self.d)   # v stays a strided view of qkv
-        if self.fused_pre_attention:
-            o = self._attention_fused(qkv, v, rope)
-        else:
-            q, k, _ = qkv.split([self.h * self.d, self.kvh * self.d, self.kvh * self.d], dim=-1)
-            q = F.rms_norm(q.reshape(-1, self.h, self.d), (self.d,), self.qk_norm_w, RMS_EPS)
-            k = F.rms_norm(k.reshape(-1, self.kvh, self.d), (self.d,), self.qk_norm_w, RMS_EPS)
-            q, k = apply_rope(q, cos, sin), apply_rope(k, cos, sin)
-            o = self.attn(q, k, v)
+        o = self._attention(F.linear(h, self.qkv_w), cos, sin, rope)
         o = F.linear(o, self.o_w)
         if self.tp_size > 1:
             torch.distributed.all_reduce(o)
@@ -156,13 +147,22 @@ class DecoderLayer(nn.Module):
             torch.distributed.all_reduce(out)
         return out, residual
 
-    def _attention_fused(self, qkv, v, rope):
-        # one launch: q/k RMSNorm + RoPE + the K/V scatter into the paged cache
-        ctx = get_context()
-        a = self.attn
-        q, k = qk_norm_rope_store(qkv, ctx.positions, rope[0], rope[1], self.qk_norm_w, self.qk_norm_w, RMS_EPS,
-                                  self.h, self.kvh, self.d, a.k_cache, a.v_cache, ctx.slot_mapping)
-        return a(q, k, v, store=False)
+    def _attention(self, qkv, cos, sin, rope):
+        """q/k RMSNorm, RoPE, K/V store and attention on the fused qkv projection output."""
+        v = qkv[:, (self.h + self.kvh) * self.d:].view(-1, self.kvh, self.d)   # v stays a strided view of qkv
+        if self.fused_pre_attention:
+            # one launch: q/k RMSNorm + RoPE + the K/V scatter into the paged cache
+            ctx = get_context()
+            a = self.attn
+            q, k = qk_norm_rope_store(qkv, ctx.positions, rope[0], rope[1], self.qk_norm_w, self.qk_norm_w, RMS_EPS,
+                                      self.h, self.kvh, self.d, a.k_cache, a.v_cache, ctx.slot_mapping)
+            return a(q, k, v, store=False)
+        # the reference's separate steps (src/myvllm/models/qwen3.py:104-110); the attention module stores K/V
+        q, k, _ = qkv.split([self.h * self.d, self.kvh * self.d, self.kvh * self.d], dim=-1)
+        q = F.rms_norm(q.reshape(-1, self.h, self.d), (self.d,), self.qk_norm_w, RMS_EPS)
+        k = F.rms_norm(k.reshape(-1, self.kvh, self.d), (self.d,), self.qk_norm_w, RMS_EPS)
+        q, k = apply_rope(q, cos, sin), apply_rope(k, cos, sin)
+        return self.attn(q, k, v)
 
     def _reduce_add_norm(self, partial, residual, gamma, comm):
         """All-reduce of the row-parallel partial sums + residual add + RMSNorm with `gamma`.
@@ -175,14 +175,12 @@ class DecoderLayer(nn.Module):
             torch.distributed.all_reduce(partial)
         return add_rms_norm(partial, residual, gamma, RMS_EPS, residual_out=residual)
 
-    def forward_fused(self, h, residual, next_gamma, rope, comm=None):
+    def forward_fused(self, h, residual, next_gamma, rope, comm=None, cos=None, sin=None):
         """CUDA path.  `h` = normalised input of this layer (all rows), `residual` = the residual stream (this
         rank's row shard when `comm` is set, all rows otherwise), `next_gamma` = weight of the norm that follows
         this layer (next layer's input norm, or the final norm).  Returns the next layer's normalised input."""
         rows = h.shape[0]
-        qkv = F.linear(h, self.qkv_w)
-        v = qkv[:, (self.h + self.kvh) * self.d:].view(-1, self.kvh, self.d)
-        o = self._attention_fused(qkv, v, rope)
+        o = self._attention(F.linear(h, self.qkv_w), cos, sin, rope)
         partial = torch.mm(o, self.o_w.t(), out=comm.input_rows(rows)) if comm is not None else F.linear(o, self.o_w)
         h = self._reduce_add_norm(partial, residual, self.post_norm_w, comm)
         act = silu_and_mul(F.linear(h, self.gate_up_w))
@@ -217,15 +215,15 @@ class Qwen3ForCausalLM(nn.Module):
             raise ValueError("Context.positions must be set before the model runs")
         fused = all(l.fused_pre_attention for l in self.layers)
         x = F.embedding(input_ids, self.embed)
-        if fused and x.is_cuda:
-            return self._forward_fused(x)
         cos, sin = (None, None) if fused else (self.rope_cos[positions], self.rope_sin[positions])
+        if x.is_cuda:
+            return self._forward_fused(x, cos, sin)
         residual = None
         for layer in self.layers:
             x, residual = layer(x, residual, cos, sin, (self.rope_cos, self.rope_sin))
         return F.rms_norm(residual + x, (x.shape[-1],), self.final_norm_w, RMS_EPS)
 
-    def _forward_fused(self, x):
+    def _forward_fused(self, x, cos=None, sin=None):
         """Every norm is fused with the add (and, under tensor parallelism, the all-reduce) in front of it, so a
         layer hands the next one its normalised input; with a communicator the residual stream is sharded by
         rows and never replicated."""
@@ -237,7 +235,7 @@ class Qwen3ForCausalLM(nn.Module):
         rope = (self.rope_cos, self.rope_sin)
         for i, layer in enumerate(self.layers):
             nxt = self.layers[i + 1].input_norm_w if i + 1 < len(self.layers) else self.final_norm_w
-            h = layer.forward_fused(h, residual, nxt, rope, comm)
+            h = layer.forward_fused(h, residual, nxt, rope, comm, cos, sin)
         return h
 
     def compute_logits(self, hidden, vocab_shard=None):

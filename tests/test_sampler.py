@@ -135,3 +135,113 @@ def test_argmax_rows_that_do_not_start_on_16_bytes():
     x = _logits(5, 3, 1001, torch.float16)
     want = oracle.argmax_rows(x.float().numpy())
     assert np.array_equal(S.argmax_rows(x.cuda(), want_keys=False, want_tokens=True)[1].cpu().numpy(), want)
+
+
+def test_zero_of_either_sign_is_one_logit_value():
+    """-0.0 and +0.0 compare equal, so torch.argmax returns the lower index; the keys must agree."""
+    x = -np.ones((3, 64), dtype=np.float32)
+    x[0, 5], x[0, 40] = -0.0, 0.0
+    x[1, 5], x[1, 40] = 0.0, -0.0
+    x[2, 33] = -0.0
+    want = torch.argmax(torch.from_numpy(x), dim=-1).numpy()
+    assert want.tolist() == [5, 5, 33]
+    assert np.array_equal(oracle.argmax_rows(x), want)
+    for shards in (1, 2, 8):
+        assert np.array_equal(oracle.argmax_sharded(x, shards), want)
+    assert oracle.make_key(-0.0, 7) == oracle.make_key(0.0, 7)
+    # merged by integer MAX of the shard keys, as the ranks do
+    keys = [oracle.shard_keys(x[:, s * 32:(s + 1) * 32], s * 32) for s in range(2)]
+    merged = [oracle.token_of_key(max(a, b)) for a, b in zip(*keys)]
+    assert merged == want.tolist()
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+def test_zero_of_either_sign_on_gpu(dtype):
+    from minivllm_b200.layers import sampler as S
+    x = -torch.ones(3, 4096, dtype=dtype)
+    x[0, 5], x[0, 3000] = -0.0, 0.0          # different threads of the row's CTA
+    x[1, 5], x[1, 3000] = 0.0, -0.0
+    x[2, 2049] = -0.0
+    want = torch.argmax(x.float(), dim=-1).numpy()
+    xd = x.cuda()
+    assert np.array_equal(S.argmax_rows(xd, want_keys=False, want_tokens=True)[1].cpu().numpy(), want)
+    keys = torch.stack([S.argmax_rows(xd[:, s * 2048:(s + 1) * 2048], index_offset=s * 2048)[0] for s in range(2)])
+    assert np.array_equal(S.decode_keys(keys.contiguous()).cpu().numpy(), want)
+    want_keys = oracle.shard_keys(x.float().numpy())
+    assert S.argmax_rows(xd)[0].cpu().tolist() == want_keys
+
+
+# ---- temperature sampling (exponential race) -----------------------------------------------------------------
+def test_philox_known_answers():
+    """Philox4x32-10 known-answer vectors of the Random123 distribution (kat_vectors), for the oracle's restatement
+    and for the library's own generator evaluated on the host."""
+    import ctypes
+    from minivllm_b200 import _cabi
+    kat = [((0, 0, 0, 0), (0, 0), (0x6627e8d5, 0xe169c58d, 0xbc57ac4c, 0x9b00dbd8)),
+           ((0xffffffff,) * 4, (0xffffffff,) * 2, (0x408f276d, 0x41c83b0e, 0xa20bc7c6, 0x6d5451fd)),
+           ((0x243f6a88, 0x85a308d3, 0x13198a2e, 0x03707344), (0xa4093822, 0x299f31d0),
+            (0xd16cfe09, 0x94fdcceb, 0x5001e420, 0x24126ea1))]
+    for ctr, key, want in kat:
+        assert oracle.philox4x32_10(ctr, key) == want
+        out = (ctypes.c_uint32 * 4)()
+        seed, step = key[0] | (key[1] << 32), ctr[2] | (ctr[3] << 32)
+        assert _cabi.lib().mv_philox4x32_10(seed, step, ctr[1], ctr[0], out) == 0
+        assert tuple(out) == want
+
+
+def test_race_oracle_draws_from_the_softmax():
+    """The restated race is a sampler of softmax(logits / T): empirical frequencies over many rows."""
+    logits = np.array([2.0, 1.0, 0.0, -1.0, 0.5, 0.5], dtype=np.float32)
+    rows, temp = 4000, 0.7
+    toks, _ = oracle.sample_rows(np.tile(logits, (rows, 1)), [temp] * rows, seed=99, step=3)
+    p = np.exp(logits / temp) / np.exp(logits / temp).sum()
+    freq = np.bincount(toks, minlength=len(logits)) / rows
+    assert np.abs(freq - p).max() < 0.03
+    greedy, _ = oracle.sample_rows(np.tile(logits, (4, 1)), [0.0] * 4, seed=1, step=0)
+    assert greedy.tolist() == [0] * 4
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+def test_sampled_tokens_match_the_race_oracle(dtype):
+    """Same seed, step, rows and columns -> same noise: the kernel's choice equals the oracle's except where the
+    oracle's two best scores are closer than the kernel's fp32 rounding; rows with temperature 0 are greedy.
+    Shards merged by MAX give the same tokens as the whole vocabulary."""
+    from minivllm_b200.layers import sampler as S
+    rows, cols = 12, 2048
+    x = _logits(6, rows, cols, dtype)
+    temps = torch.tensor([0.6, 1.0, 0.0, 2.5] * 3, dtype=torch.float32)
+    step = torch.tensor([41], dtype=torch.int64, device="cuda")
+    want, scores = oracle.sample_rows(x.float().numpy(), temps.numpy(), seed=1234, step=41)
+    xd, td = x.cuda(), temps.cuda()
+    got = S.sampled_tokens(xd, td, 1234, step).cpu().numpy()
+    for r in range(rows):
+        if got[r] != want[r]:
+            top2 = np.sort(scores[r])[-2:]
+            assert top2[1] - top2[0] < 1e-4 * max(1.0, abs(top2[1])), f"row {r}: {got[r]} vs {want[r]}"
+    assert np.array_equal(got[2::4], oracle.argmax_rows(x.float().numpy())[2::4])
+    for shards in (2, 8):
+        w = cols // shards
+        keys = torch.stack([S.sample_rows(xd[:, s * w:(s + 1) * w], td, 1234, step, index_offset=s * w)[0]
+                            for s in range(shards)])
+        assert np.array_equal(S.decode_keys(keys.contiguous()).cpu().numpy(), got)
+    step.add_(1)
+    again = S.sampled_tokens(xd, td, 1234, step).cpu().numpy()
+    assert not np.array_equal(again[0::4], got[0::4]) or not np.array_equal(again[1::4], got[1::4])   # new noise
+    assert np.array_equal(again[2::4], got[2::4])                                                   # greedy rows
+
+
+@pytest.mark.gpu
+def test_sampled_token_frequencies_follow_the_softmax():
+    from minivllm_b200.layers import sampler as S
+    logits = torch.tensor([2.0, 1.0, 0.0, -1.0, 0.5, 0.5, -3.0, 1.5], dtype=torch.float32)
+    rows, temp = 40000, 0.6
+    x = logits.to(torch.bfloat16).repeat(rows, 1).cuda()
+    t = torch.full((rows,), temp, dtype=torch.float32, device="cuda")
+    step = torch.zeros(1, dtype=torch.int64, device="cuda")
+    toks = S.sampled_tokens(x, t, 7, step).cpu().numpy()
+    z = logits.to(torch.bfloat16).float().numpy() / temp
+    p = np.exp(z) / np.exp(z).sum()
+    freq = np.bincount(toks, minlength=8) / rows
+    assert np.abs(freq - p).max() < 0.01, (freq, p)
