@@ -400,6 +400,23 @@ def case_argmax(device, pk, iters=20):
     return _hbm(ms, x.numel() * 2 + 512 * 8, pk, torch_argmax_us=ref * 1e3, same_tokens_as_torch=same)
 
 
+def case_sample(device, pk, iters=20):
+    """Temperature sampling tail (exponential race, Philox noise): 512 rows x 151,936 columns bf16, T = 0.6."""
+    from minivllm_b200.layers import sampler as S
+    g = torch.Generator(device=device).manual_seed(5)
+    x = torch.randn(512, 151936, generator=g, device=device, dtype=torch.float32).to(torch.bfloat16)
+    temps = torch.full((512,), 0.6, dtype=torch.float32, device=device)
+    step = torch.zeros(1, dtype=torch.int64, device=device)
+    ms = _time_calls([lambda: S.sample_rows(x, temps, 1234, step, want_keys=False, want_tokens=True)], iters, 3)
+
+    def torch_race():       # what it replaces: softmax of fp32 logits, an exponential draw, a division, an argmax
+        p = torch.softmax(x.float() / temps.unsqueeze(-1), dim=-1)
+        return p.div_(torch.empty_like(p).exponential_(1).clamp_min_(1e-10)).argmax(dim=-1)
+    ref = _time_calls([torch_race], max(2, iters // 4), 2)
+    return _hbm(ms, x.numel() * 2 + 512 * 8, pk, torch_softmax_race_us=ref * 1e3,
+                note="compute-bound (Philox + two logarithms per logit); the HBM figure is for scale only")
+
+
 def case_add_rmsnorm(device, pk, iters=20):
     """Fused residual add + RMSNorm (single-rank form): 16,384 rows x 4096 bf16, residual updated in place."""
     from minivllm_b200.layers.layernorm import add_rms_norm
@@ -432,6 +449,7 @@ OP_CASES = {
     "prefill_paged_bf16_16seq_half_cached": case_prefill_paged,
     "qk_norm_rope_store_16384tok": case_pre_attention,
     "argmax_rows_512x151936": case_argmax,
+    "sample_rows_512x151936": case_sample,
     "add_rmsnorm_16384x4096": case_add_rmsnorm,
     "silu_mul_16384x12288": case_silu_mul,
 }

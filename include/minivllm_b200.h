@@ -172,6 +172,14 @@ int mv_prefill_varlen(void* out, const void* q, const void* k, const void* v,
  * offsets (src/myvllm/layers/attention.py:135-137,171,194).  block_size must
  * divide 128 (multiple of 8) or be a multiple of 128.  Same error_word
  * contract as mv_prefill_varlen.
+ * Precondition: every row of every cache block that a table names must hold
+ * FINITE values, also the rows past a sequence's last key (the rest of its
+ * last block) and block 0 (read in place of a missing table entry).  Such
+ * rows get weight exactly 0, but their V values still pass through the
+ * tensor-core product, and 0 x NaN or 0 x Inf is NaN.  Allocate the pool
+ * zero-initialised (the engine does); blocks that were used before hold
+ * finite stale values and are fine.  mv_paged_decode has no such
+ * precondition (it zero-fills rows it does not use).
  */
 int mv_prefill_paged(void* out, const void* q, int64_t q_stride_tok,
                      const void* k_cache, const void* v_cache,

@@ -40,7 +40,7 @@ def build(verbose=False, force=False):
                 print(" ".join(cmd), flush=True)
             subprocess.check_call(cmd)
     if force or _stale(LIB, objs):
-        cmd = [nvcc, "-shared", "-o", LIB] + objs + ["-lcudart", "-lcuda"]
+        cmd = [nvcc, "-shared", "-o", LIB] + objs + ["-lcudart"]
         if verbose:
             print(" ".join(cmd), flush=True)
         subprocess.check_call(cmd)

@@ -166,38 +166,58 @@ store_kv_quant_kernel(const uint4* __restrict__ key, const uint4* __restrict__ v
   uint32_t c = static_cast<uint32_t>(i - t * chunks_per_row);
   const int64_t t_step = stride / chunks_per_row;
   const uint32_t c_step = static_cast<uint32_t>(stride - t_step * chunks_per_row);
-  for (int64_t r = 0; r < rounds; ++r, i += stride) {
-    bool live = false;
-    int64_t slot = -1;
-    uint4 kraw = make_uint4(0, 0, 0, 0), vraw = make_uint4(0, 0, 0, 0);
-    if (i < total_chunks) {
-      slot = __ldg(slot_mapping + t);
+  // Software pipeline, one round deep: the loads of round r+1 are issued before round r is quantised, so the
+  // per-row dependency chain (maximum -> shuffle -> scale -> reciprocal -> codes) overlaps a load latency
+  // instead of following it.
+  auto fetch = [&](int64_t idx, int64_t tok, uint32_t chunk, int64_t& slot, bool& live, uint4& kraw, uint4& vraw) {
+    live = false;
+    slot = -1;
+    kraw = make_uint4(0, 0, 0, 0);
+    vraw = make_uint4(0, 0, 0, 0);
+    if (idx < total_chunks) {
+      slot = __ldg(slot_mapping + tok);
       live = slot >= 0 && slot < num_slots;
       if (live) {
-        kraw = ld_stream16(key + t * k_stride16 + c);
-        vraw = ld_stream16(value + t * v_stride16 + c);
+        kraw = ld_stream16(key + tok * k_stride16 + chunk);
+        vraw = ld_stream16(value + tok * v_stride16 + chunk);
       }
     }
-    uint2 kc, vc;
-    __half ks, vs;
-    quant_chunk<T, GROUP>(kraw, kc, ks);
-    quant_chunk<T, GROUP>(vraw, vc, vs);
-    if (live) {
-      const int64_t dst = slot * chunks_per_row + c;  // 8-byte units of the int8 row
-      st_global8(k_codes + dst, kc);
-      st_global8(v_codes + dst, vc);
-      if ((c & (GROUP - 1)) == 0) {
-        const int64_t sidx = slot * num_kv_heads + c / GROUP;
-        k_scale[sidx] = ks;
-        v_scale[sidx] = vs;
-      }
-    }
+  };
+  auto advance = [&]() {
+    i += stride;
     t += t_step;
     c += c_step;
     if (c >= chunks_per_row) {
       c -= chunks_per_row;
       ++t;
     }
+  };
+  int64_t slot, slot_n;
+  bool live, live_n;
+  uint4 kraw, vraw, kraw_n, vraw_n;
+  fetch(i, t, c, slot, live, kraw, vraw);
+  for (int64_t r = 0; r < rounds; ++r) {
+    const uint32_t c_now = c;
+    advance();
+    fetch(r + 1 < rounds ? i : total_chunks, t, c, slot_n, live_n, kraw_n, vraw_n);
+    uint2 kc, vc;
+    __half ks, vs;
+    quant_chunk<T, GROUP>(kraw, kc, ks);
+    quant_chunk<T, GROUP>(vraw, vc, vs);
+    if (live) {
+      const int64_t dst = slot * chunks_per_row + c_now;  // 8-byte units of the int8 row
+      st_global8(k_codes + dst, kc);
+      st_global8(v_codes + dst, vc);
+      if ((c_now & (GROUP - 1)) == 0) {
+        const int64_t sidx = slot * num_kv_heads + c_now / GROUP;
+        k_scale[sidx] = ks;
+        v_scale[sidx] = vs;
+      }
+    }
+    slot = slot_n;
+    live = live_n;
+    kraw = kraw_n;
+    vraw = vraw_n;
   }
 }
 

@@ -178,3 +178,12 @@ def test_prefill_wait_that_runs_out_is_reported():
     assert _call_c_abi(d, dtype, out, word) == 0          # the injection was for one launch only
     assert int(word.item()) == 0
     _close(out.float().cpu(), _oracle(d, dtype), dtype)
+
+
+def test_prefill_benchmark_configuration_exactly():
+    """The prefill configuration of the benchmark plan, as `bench.py` times it: 32 sequences, lengths uniform in
+    [128, 2048] (34,277 tokens with this seed), 32 query / 8 KV heads, head_dim 128, bf16 -- every sequence, every
+    head, every row against the fp32 oracle."""
+    d = synth.prefill_inputs()                      # the defaults ARE that configuration (seed 1)
+    assert d["q"].shape[0] == 34277 and d["num_heads"] == 32 and d["num_kv_heads"] == 8
+    _close(_gpu(d, torch.bfloat16), _oracle(d, torch.bfloat16), torch.bfloat16)

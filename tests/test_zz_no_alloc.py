@@ -45,10 +45,15 @@ def _run_both(d, dtype):
     ws = torch.empty(need, dtype=torch.uint8, device=DEV)
     assert lib.mv_paged_decode(*head, ws.data_ptr(), need, code, stream) == 0, lib.mv_last_error_string()
     head[0] = out_new.data_ptr()
-    before = torch.cuda.memory_allocated(DEV)
+    # warm-up call (the first call on a device resolves the array's address), then the checked one: the
+    # driver's count of free device memory must not move, which would also show an allocation made inside
+    # the library, invisible to torch's allocator statistics
     assert lib.mv_paged_decode_static(*head, code, stream) == 0, lib.mv_last_error_string()
     torch.cuda.synchronize()
-    assert torch.cuda.memory_allocated(DEV) == before
+    free_before = torch.cuda.mem_get_info(DEV)[0]
+    assert lib.mv_paged_decode_static(*head, code, stream) == 0, lib.mv_last_error_string()
+    torch.cuda.synchronize()
+    assert torch.cuda.mem_get_info(DEV)[0] == free_before
     del keep
     return out_ref, out_new
 
@@ -68,6 +73,43 @@ def test_static_scratch_decode_matches_workspace_decode_twice():
     # and the first problem again gives the first answer again
     ref3, new3 = _run_both(d1, torch.float16)
     assert torch.equal(new3, new1) and torch.equal(ref3, new3)
+
+
+def test_static_scratch_decode_is_within_tolerance_of_the_oracle():
+    from oracle import attention_oracle as oracle
+    d = synth.decode_inputs(seed=72, batch=5, ctx_lo=2000, ctx_hi=5000, num_heads=8, num_kv_heads=4, head_dim=128,
+                            block_size=256)
+    _, new = _run_both(d, torch.float16)
+    r = lambda x: x.to(torch.float16).float()
+    want = oracle.paged_attention_decode(r(d["q"]), r(d["k_cache"]), r(d["v_cache"]), d["block_tables"],
+                                         d["context_lens"], d["scale"], 8, 4, 128, 256)
+    assert float((new.float().cpu() - want).abs().max()) < 2e-3
+
+
+def test_static_scratch_decode_reads_an_int8_cache_too():
+    """The k_scale / v_scale route through the allocation-free entry point, against the workspace entry point."""
+    from minivllm_b200.layers import attention as A
+    lib = _cabi.lib()
+    d = synth.decode_inputs(seed=73, batch=4, ctx_lo=1500, ctx_hi=4000, num_heads=8, num_kv_heads=2, head_dim=128,
+                            block_size=256)
+    dt = torch.float16
+    nb, bs, kvh, hd = d["k_cache"].shape
+    kq, vq = (torch.zeros(nb, bs, kvh, hd, dtype=torch.int8, device=DEV) for _ in range(2))
+    ks, vs = (torch.zeros(nb, bs, kvh, dtype=torch.float16, device=DEV) for _ in range(2))
+    slots = torch.arange(nb * bs, dtype=torch.int64, device=DEV)
+    A.store_kvcache(d["k_cache"].reshape(-1, kvh, hd).to(dt).to(DEV), d["v_cache"].reshape(-1, kvh, hd).to(dt).to(DEV),
+                    kq, vq, slots, bs, k_scale=ks, v_scale=vs)
+    q, bt, cl = d["q"].to(dt).to(DEV), d["block_tables"].to(DEV), d["context_lens"].to(DEV)
+    stream = torch.cuda.current_stream().cuda_stream
+    outs = [torch.zeros_like(q) for _ in range(2)]
+    need = lib.mv_paged_decode_workspace_bytes(4, 8, 2, 128, bt.shape[1], 256)
+    ws = torch.empty(need, dtype=torch.uint8, device=DEV)
+    head = lambda o: [o.data_ptr(), q.data_ptr(), kq.data_ptr(), vq.data_ptr(), ks.data_ptr(), vs.data_ptr(),
+                      bt.data_ptr(), bt.stride(0), bt.shape[1], cl.data_ptr(), 1, 4, 8, 2, 128, 256, nb, d["scale"]]
+    assert lib.mv_paged_decode(*head(outs[0]), ws.data_ptr(), need, 0, stream) == 0, lib.mv_last_error_string()
+    assert lib.mv_paged_decode_static(*head(outs[1]), 0, stream) == 0, lib.mv_last_error_string()
+    torch.cuda.synchronize()
+    assert torch.equal(outs[0], outs[1]) and float(outs[0].float().abs().max()) > 0
 
 
 def test_static_scratch_refuses_oversized_problems():
