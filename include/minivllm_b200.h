@@ -71,6 +71,11 @@ int mv_store_kvcache(const void* key, const void* value,
  * Bytes of scratch mv_paged_decode needs for the given problem (split-K
  * partial results); depends on shapes only, never on context_lens values.
  * Returns -1 for an invalid shape.
+ * The first 64 KiB of the scratch hold arrival counters (which piece of a
+ * split sequence was written last): they must be ZERO when the buffer is
+ * first used, and every call leaves them zero, so fill the buffer with zeros
+ * once when it is allocated.  One buffer may serve calls of any shapes, one
+ * at a time (calls that overlap on the GPU need buffers of their own).
  */
 int64_t mv_paged_decode_workspace_bytes(int batch, int num_heads,
                                         int num_kv_heads, int head_dim,

@@ -26,4 +26,4 @@ int check_launch(const char* what) {
 
 extern "C" const char* mv_last_error_string(void) { return mv::g_last_error; }
 
-extern "C" int mv_abi_version(void) { return 1; }
+extern "C" int mv_abi_version(void) { return 2; }

@@ -20,9 +20,12 @@
 //   * the G query heads of the KV head are the (zero-padded) 16 rows of an
 //     m16n8k16 MMA: S = Q K^T and O += P V run on the tensor cores with fp32
 //     accumulation, softmax statistics in fp32 registers, exp2 domain.
-//   * warps merge through shared memory; a sequence with one chunk writes its
-//     output directly, otherwise partial (m, l, O) go to the caller's scratch
-//     and a small combine kernel reduces them in a fixed order.
+//   * warps merge through shared memory; a sequence with one piece writes its
+//     output directly, otherwise partial (m, l, O) go to the caller's scratch and
+//     the CTA that writes the last piece of a (sequence, KV head) reduces them in
+//     item order (an arrival counter per cell; nobody waits).  Only when a
+//     problem has more cells than the scratch reserves counters for does a
+//     separate small combine kernel do that.
 // HBM-bound: algorithmic bytes = sum(ctx) * num_kv_heads * head_dim * 2 *
 // sizeof(elem) + q and out.
 #include "paged_decode.cuh"
@@ -62,6 +65,7 @@ paged_decode_kernel(const DecodeParams p) {
   extern __shared__ __align__(128) unsigned char smem[];
   __shared__ long long s_red[kDecWarps];
   __shared__ uint32_t s_mask[kDecWarps][kDecStages];
+  __shared__ int s_last;
   int* s_start = reinterpret_cast<int*>(smem + S::kRingBytes + (kStream ? S::kStreamMergeBytes : 0));
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -316,6 +320,7 @@ paged_decode_kernel(const DecodeParams p) {
       __syncthreads();
       merge_and_write<T, D>(p, sO, sML, S::kMergeStride, rows_valid, h0, b, item, nsplit, R);
       __syncthreads();  // the buffer is free for the next item
+      combine_if_last<T, D>(p, s_start, plan, b, b * ydim + kvh * p.mtiles + mt, h0, rows_valid, nsplit, &s_last);
     } else {
       __syncthreads();  // the ring is idle now
       float* sO = reinterpret_cast<float*>(smem);
@@ -337,6 +342,7 @@ paged_decode_kernel(const DecodeParams p) {
       __syncthreads();
       merge_and_write<T, D>(p, sO, sML, S::kMergeStride, rows_valid, h0, b, item, nsplit);
       __syncthreads();  // the ring is handed back to the pipelines
+      combine_if_last<T, D>(p, s_start, plan, b, b * ydim + kvh * p.mtiles + mt, h0, rows_valid, nsplit, &s_last);
     }
   }
   if constexpr (kStream) cp_async_wait<0>();   // only empty groups are left
@@ -368,15 +374,22 @@ paged_decode_combine_kernel(const DecodeParams p) {
 }
 
 struct DecodeLayout {
-  int64_t binfo_off, ml_off, o_off, total;
+  int64_t arrivals_off, binfo_off, ml_off, o_off, total;
+  bool folded;   // arrival counters fit: the last piece's CTA reduces, no combine launch
 };
 static DecodeLayout decode_layout(int batch, int num_heads, int num_kv_heads, int head_dim, int max_blocks,
                                   int block_size) {
+  (void)max_blocks;
+  (void)block_size;
   const int mtiles = (num_heads / num_kv_heads + 15) / 16;
   const int64_t items = decode_items_max(batch, num_kv_heads, mtiles);
   DecodeLayout L;
-  L.binfo_off = 0;
-  L.ml_off = ((static_cast<int64_t>(batch) * 8 + 255) / 256) * 256;
+  // The counters sit first and always take the same room, so that calls of different shapes that share one
+  // scratch buffer never write anything but counters there.
+  L.arrivals_off = 0;
+  L.folded = static_cast<int64_t>(batch) * num_kv_heads * mtiles <= kDecodeArrivalCells;
+  L.binfo_off = static_cast<int64_t>(kDecodeArrivalCells) * 4;
+  L.ml_off = L.binfo_off + ((static_cast<int64_t>(batch) * 8 + 255) / 256) * 256;
   L.o_off = L.ml_off + ((items * num_heads * 2 * 4 + 255) / 256) * 256;
   L.total = L.o_off + items * num_heads * head_dim * 4;
   return L;
@@ -416,7 +429,7 @@ static int launch_decode(const DecodeParams& p, cudaStream_t st) {
                       kDecCtasPerSM * (smem_stream + kStaticSmem + 1024) <= 227 * 1024;
   int rc = stream ? launch_decode_variant<T, D, true>(p, smem_stream, st)
                   : launch_decode_variant<T, D, false>(p, smem, st);
-  if (rc) return rc;
+  if (rc || p.arrivals) return rc;
   paged_decode_combine_kernel<T, D><<<dim3(p.batch, p.num_kv_heads), 128, 0, st>>>(p);
   return check_launch("paged_decode_combine_kernel");
 }
@@ -472,13 +485,14 @@ extern "C" int mv_paged_decode(void* out, const void* q, const void* k_cache, co
   p.scale_log2 = scale * 1.4426950408889634f;
   p.target_items = decode_target_items(num_kv_heads, p.mtiles);
   unsigned char* ws = static_cast<unsigned char*>(workspace);
+  p.arrivals = L.folded ? reinterpret_cast<unsigned*>(ws + L.arrivals_off) : nullptr;
   p.binfo = reinterpret_cast<int2*>(ws + L.binfo_off);
   p.part_ml = reinterpret_cast<float*>(ws + L.ml_off);
   p.part_o = reinterpret_cast<float*>(ws + L.o_off);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (k_scale) {
     const int rc = dtype == MV_F16 ? launch_decode_int8<__half>(p, st) : launch_decode_int8<__nv_bfloat16>(p, st);
-    if (rc) return rc;
+    if (rc || p.arrivals) return rc;
     if (dtype == MV_F16) paged_decode_combine_kernel<__half, 128><<<dim3(batch, num_kv_heads), 128, 0, st>>>(p);
     else paged_decode_combine_kernel<__nv_bfloat16, 128><<<dim3(batch, num_kv_heads), 128, 0, st>>>(p);
     return check_launch("paged_decode_combine_kernel");

@@ -34,7 +34,10 @@ struct DecodeParams {
   int64_t num_blocks;
   float scale_log2;
   int target_items;
-  int2* binfo;      // per sequence: (first item, number of items)
+  int2* binfo;      // per sequence: (first item, number of items); read by the separate combine kernel only
+  unsigned* arrivals;  // per (sequence, KV head, row tile): pieces of a split sequence that have been written;
+                       // zero between launches.  Null when the problem has more such cells than the scratch
+                       // reserves: the pieces are then reduced by the separate combine kernel.
   float* part_ml;   // (item, head, 2)
   float* part_o;    // (item, head, D)
 };
@@ -207,6 +210,46 @@ __device__ __forceinline__ void merge_and_write(const DecodeParams& p, const flo
       if (d == 0) { p.part_ml[pi * 2] = M; p.part_ml[pi * 2 + 1] = L; }
     }
   }
+}
+
+// A sequence that spans segments leaves one partial result per piece.  The CTA that writes the LAST piece of a
+// (sequence, KV head, row tile) reduces them all, in item order (so the result does not depend on which CTA
+// that was), and writes the output rows: no second launch, and no CTA ever waits for another.  Called by the
+// whole CTA after merge_and_write and a __syncthreads().  `s_last` is one int of shared memory.
+constexpr int kDecodeArrivalCells = 16384;                       // 64 KiB of counters at the start of the scratch
+template <typename T, int D>
+__device__ __forceinline__ void combine_if_last(const DecodeParams& p, const int* s_tok, const DecodePlan& plan, int b,
+                                                int cell, int h0, int rows_valid, int nsplit, int* s_last) {
+  if (p.arrivals == nullptr || nsplit <= 1) return;             // uniform over the CTA
+  if (threadIdx.x == 0) {
+    __threadfence();                                              // this CTA's partial rows (ordered by the barrier)
+    const bool last = atomicAdd(&p.arrivals[cell], 1u) == static_cast<unsigned>(nsplit - 1);
+    if (last) {
+      __threadfence();                                            // ... and those of the CTAs counted before it
+      p.arrivals[cell] = 0;                                       // zero again for the next launch
+    }
+    *s_last = last;
+  }
+  __syncthreads();
+  if (*s_last) {
+    const int2 info = seq_items(s_tok, plan, b);
+    for (int idx = threadIdx.x; idx < rows_valid * D; idx += kDecThreads) {
+      const int h = h0 + idx / D, d = idx % D;
+      float M = kNegBig;
+      for (int s = 0; s < info.y; ++s)
+        M = fmaxf(M, __ldcg(p.part_ml + (static_cast<int64_t>(info.x + s) * p.num_heads + h) * 2));
+      float acc = 0.f, L = 0.f;
+      for (int s = 0; s < info.y; ++s) {
+        const int64_t pi = static_cast<int64_t>(info.x + s) * p.num_heads + h;
+        const float wgt = fast_exp2(__ldcg(p.part_ml + pi * 2) - M);
+        acc += wgt * __ldcg(p.part_o + pi * D + d);
+        L += wgt * __ldcg(p.part_ml + pi * 2 + 1);
+      }
+      const float r = L > 0.f ? acc / L : 0.f;
+      static_cast<T*>(p.out)[(static_cast<int64_t>(b) * p.num_heads + h) * D + d] = Elem<T>::from_f(r);
+    }
+  }
+  __syncthreads();                                                // s_last is reused by the next item
 }
 
 // Launch of the int8-cache kernel (paged_decode_int8.cu); head_dim 128 only.

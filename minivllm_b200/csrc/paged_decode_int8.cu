@@ -72,6 +72,7 @@ paged_decode_int8_kernel(const DecodeParams p) {
   extern __shared__ __align__(128) unsigned char smem[];
   __shared__ long long s_red[kDecWarps];
   __shared__ uint32_t s_mask[kDecWarps][kQStages][2];  // [0]: live rows of the tile, [1]: rows whose scale index is odd
+  __shared__ int s_last;
   int* s_start = reinterpret_cast<int*>(smem + S::kRingBytes);
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -334,6 +335,7 @@ paged_decode_int8_kernel(const DecodeParams p) {
     __syncthreads();
     merge_and_write<T, D>(p, sO, sML, S::kMergeStride, rows_valid, h0, b, item, nsplit);
     __syncthreads();
+    combine_if_last<T, D>(p, s_start, plan, b, b * ydim + kvh * p.mtiles + mt, h0, rows_valid, nsplit, &s_last);
   }
 }
 

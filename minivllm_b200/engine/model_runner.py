@@ -312,7 +312,7 @@ class ModelRunner:
         need = _cabi.lib().mv_paged_decode_workspace_bytes(max_bs, c.num_heads // self.world_size,
                                                            c.num_kv_heads // self.world_size, c.head_dim,
                                                            self.max_blocks_per_seq, self.block_size)
-        self.decode_workspace = torch.empty(max(need, 1), dtype=torch.uint8, device=self.device)
+        self.decode_workspace = torch.zeros(max(need, 1), dtype=torch.uint8, device=self.device)
         sizes = [b for b in [1, 2, 4, 8] if b <= max_bs] + list(range(16, max_bs + 1, 16))
         if max_bs not in sizes:
             sizes.append(max_bs)

@@ -26,10 +26,11 @@ _workspaces = {}
 
 
 def _decode_workspace(device, nbytes):
-    """Grow-only scratch per device for the split-K partial results."""
+    """Grow-only scratch per device for the split-K partial results (zero-filled: its first 64 KiB are the
+    arrival counters of split sequences, which every call leaves zero)."""
     ws = _workspaces.get(device)
     if ws is None or ws.numel() < nbytes:
-        ws = torch.empty(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
+        ws = torch.zeros(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
         _workspaces[device] = ws
     return ws
 

@@ -42,7 +42,7 @@ def _run_both(d, dtype):
     keep, head = _args(d, dtype, out_ref)
     need = lib.mv_paged_decode_workspace_bytes(shape[0], d["num_heads"], d["num_kv_heads"], d["head_dim"],
                                                d["block_tables"].shape[1], d["block_size"])
-    ws = torch.empty(need, dtype=torch.uint8, device=DEV)
+    ws = torch.zeros(need, dtype=torch.uint8, device=DEV)   # the counters at its start must begin at zero
     assert lib.mv_paged_decode(*head, ws.data_ptr(), need, code, stream) == 0, lib.mv_last_error_string()
     head[0] = out_new.data_ptr()
     # warm-up call (the first call on a device resolves the array's address), then the checked one: the
@@ -103,7 +103,7 @@ def test_static_scratch_decode_reads_an_int8_cache_too():
     stream = torch.cuda.current_stream().cuda_stream
     outs = [torch.zeros_like(q) for _ in range(2)]
     need = lib.mv_paged_decode_workspace_bytes(4, 8, 2, 128, bt.shape[1], 256)
-    ws = torch.empty(need, dtype=torch.uint8, device=DEV)
+    ws = torch.zeros(need, dtype=torch.uint8, device=DEV)   # the counters at its start must begin at zero
     head = lambda o: [o.data_ptr(), q.data_ptr(), kq.data_ptr(), vq.data_ptr(), ks.data_ptr(), vs.data_ptr(),
                       bt.data_ptr(), bt.stride(0), bt.shape[1], cl.data_ptr(), 1, 4, 8, 2, 128, 256, nb, d["scale"]]
     assert lib.mv_paged_decode(*head(outs[0]), ws.data_ptr(), need, 0, stream) == 0, lib.mv_last_error_string()
