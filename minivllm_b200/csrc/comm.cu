@@ -719,3 +719,40 @@ extern "C" int mv_silu_mul(void* out, const void* gate_up, int64_t gate_up_strid
   else return fail(MV_ERR_DTYPE, "silu_mul: dtype %d", dtype);
   return check_launch("silu_mul");
 }
+
+// Measurement hook (not in the public header): a plain copy between this rank's buffers and the next rank's,
+// with 16-byte loads and stores, `unroll` independent vectors in flight per thread.  mode 0 pulls the peer's
+// input buffer into the local gather buffer, mode 1 pushes the local input buffer into the peer's gather buffer.
+// It answers "what can plain peer loads / stores reach on this link" next to the fused kernel's figure.
+namespace mv {
+template <int U>
+__global__ void __launch_bounds__(512) peer_copy_kernel(const uint4* __restrict__ src, uint4* __restrict__ dst, size_t nvec) {
+  const size_t stride = static_cast<size_t>(gridDim.x) * blockDim.x;
+  for (size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < nvec; i += stride * U) {
+    uint4 v[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u)
+      if (i + u * stride < nvec) v[u] = ld_global16(src + i + u * stride);
+#pragma unroll
+    for (int u = 0; u < U; ++u)
+      if (i + u * stride < nvec) st_global16(dst + i + u * stride, v[u]);
+  }
+}
+}  // namespace mv
+
+extern "C" int mv_debug_peer_copy(void* comm, int mode, int64_t bytes, int blocks, int unroll, void* stream) {
+  Comm* c = static_cast<Comm*>(comm);
+  if (!c || !c->connected || c->emulated) return fail(MV_ERR_SHAPE, "peer_copy: needs a connected multi-GPU communicator");
+  if (bytes <= 0 || bytes > c->data_bytes || bytes % 16) return fail(MV_ERR_SHAPE, "peer_copy: bad size");
+  const int peer = (c->rank + 1) % c->world;
+  const size_t out_off = kCtrlBytes + round256(static_cast<size_t>(c->data_bytes));
+  const uint4* src = reinterpret_cast<const uint4*>(c->region[mode == 0 ? peer : c->rank] + kCtrlBytes);
+  uint4* dst = reinterpret_cast<uint4*>(c->region[mode == 0 ? c->rank : peer] + out_off);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const size_t nvec = static_cast<size_t>(bytes) / 16;
+  if (unroll >= 8) peer_copy_kernel<8><<<blocks, 512, 0, st>>>(src, dst, nvec);
+  else if (unroll >= 4) peer_copy_kernel<4><<<blocks, 512, 0, st>>>(src, dst, nvec);
+  else if (unroll >= 2) peer_copy_kernel<2><<<blocks, 512, 0, st>>>(src, dst, nvec);
+  else peer_copy_kernel<1><<<blocks, 512, 0, st>>>(src, dst, nvec);
+  return check_launch("peer_copy_kernel");
+}
