@@ -369,8 +369,8 @@ def case_prefill_paged(device, pk, iters=10):
             "error_word": A.prefill_error_code(device)}
 
 
-def case_pre_attention(device, pk, iters=20):
-    """Fused q/k RMSNorm + RoPE + K/V store: 16,384 tokens, 32q/8kv heads of 128, bf16."""
+def case_pre_attention(device, pk, iters=20, int8=False):
+    """Fused q/k RMSNorm + RoPE + K/V store: 16,384 tokens, 32q/8kv heads of 128, bf16 (int8: quantising store)."""
     from minivllm_b200.layers import attention as A
     g = torch.Generator().manual_seed(5)
     tokens, H, KVH, D = 16384, 32, 8, 128
@@ -381,11 +381,15 @@ def case_pre_attention(device, pk, iters=20):
     inv = 1.0 / (1e6 ** (torch.arange(0, D, 2).float() / D))
     ang = torch.arange(2048).float()[:, None] * inv[None, :]
     cos, sin = torch.cos(ang).to(device), torch.sin(ang).to(device)
-    kc = torch.zeros(128, 256, KVH, D, dtype=bf, device=device)
+    kc = torch.zeros(128, 256, KVH, D, dtype=torch.int8 if int8 else bf, device=device)
     vc = torch.zeros_like(kc)
+    ks = torch.zeros(128, 256, KVH, dtype=torch.float16, device=device) if int8 else None
+    vs = torch.zeros_like(ks) if int8 else None
     slots = torch.randperm(128 * 256, generator=g)[:tokens].to(device)
-    ms = _time_calls([lambda: A.qk_norm_rope_store(qkv, pos, cos, sin, gam, gam, 1e-5, H, KVH, D, kc, vc, slots)], iters, 3)
-    nbytes = tokens * ((H + 2 * KVH) * D * 2 + (H + KVH) * D * 2 + 2 * KVH * D * 2 + 16)
+    ms = _time_calls([lambda: A.qk_norm_rope_store(qkv, pos, cos, sin, gam, gam, 1e-5, H, KVH, D, kc, vc, slots,
+                                                   k_scale=ks, v_scale=vs)], iters, 3)
+    cache_row = (D + 2) if int8 else D * 2
+    nbytes = tokens * ((H + 2 * KVH) * D * 2 + (H + KVH) * D * 2 + 2 * KVH * cache_row + 16)
     return _hbm(ms, nbytes, pk)
 
 
@@ -415,6 +419,24 @@ def case_sample(device, pk, iters=20):
     ref = _time_calls([torch_race], max(2, iters // 4), 2)
     return _hbm(ms, x.numel() * 2 + 512 * 8, pk, torch_softmax_race_us=ref * 1e3,
                 note="compute-bound (Philox + two logarithms per logit); the HBM figure is for scale only")
+
+
+def case_allreduce_emulated(device, pk, iters=20):
+    """Fused all-reduce + residual + RMSNorm, EMULATED world of 8 ranks on one GPU (one cooperative launch runs
+    every rank's blocks): 128 rows x 4096 bf16.  A single-GPU stand-in for profilers (a multi-rank run may not be
+    profiled); link traffic is replaced by local memory traffic, so only the instruction-level figures carry over."""
+    from minivllm_b200.layers.allreduce import EmulatedCommunicator
+    world, rows, hidden = 8, 128, 4096
+    comm = EmulatedCommunicator(world, rows, hidden, torch.bfloat16, device)
+    g = torch.Generator(device=device).manual_seed(3)
+    for r in range(world):
+        comm.inputs[r][:rows].copy_(torch.randn(rows, hidden, generator=g, device=device, dtype=torch.float32))
+    shards = torch.zeros(world, rows // world, hidden, dtype=torch.bfloat16, device=device)
+    gamma = torch.ones(hidden, dtype=torch.bfloat16, device=device)
+    ms = _time_calls([lambda: comm.allreduce_residual_rmsnorm(rows, shards, gamma, 1e-5)], iters, 3)
+    err = int(comm.error_word.item())
+    comm.close()
+    return {"us_per_call": ms * 1e3, "ranks_emulated": world, "rows": rows, "error_word": err}
 
 
 def case_add_rmsnorm(device, pk, iters=20):
@@ -448,9 +470,11 @@ OP_CASES = {
     "prefill_varlen_bf16_256seq_64_512": lambda device, pk, iters=20: case_prefill(device, pk, iters, 256, 64, 512),
     "prefill_paged_bf16_16seq_half_cached": case_prefill_paged,
     "qk_norm_rope_store_16384tok": case_pre_attention,
+    "qk_norm_rope_store_int8_16384tok": lambda device, pk, iters=20: case_pre_attention(device, pk, iters, int8=True),
     "argmax_rows_512x151936": case_argmax,
     "sample_rows_512x151936": case_sample,
     "add_rmsnorm_16384x4096": case_add_rmsnorm,
+    "allreduce_emulated_8ranks_128rows": case_allreduce_emulated,
     "silu_mul_16384x12288": case_silu_mul,
 }
 

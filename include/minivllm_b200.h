@@ -248,7 +248,10 @@ int mv_update_block_tables(const int32_t* updates, int num_updates,
  * cos/sin tables (max_position, 64) at positions[t], then q -> q_out
  * (tokens, num_heads, 128), k -> k_out (tokens, num_kv_heads, 128) and, when
  * slot_mapping is non-null, k and v -> the paged caches at slot_mapping[t]
- * (negative = skip), i.e. store_kvcache fused in.
+ * (negative = skip), i.e. store_kvcache fused in.  With k_scale / v_scale
+ * non-null the caches are int8 and the rows are quantised on the way in, with
+ * the arithmetic and layouts of mv_store_kvcache (codes and fp16 scales equal
+ * what mv_store_kvcache writes for k_out and v).
  * Replaces, in one launch: src/myvllm/models/qwen3.py:104-108 (rms_norm of q
  * and k, rotary_emb), layers/layernorm.py:10-17, layers/rotary_embedding.py
  * :4-23,77-83 and the store_kvcache call of layers/attention.py:498-510.
@@ -258,7 +261,8 @@ int mv_qk_norm_rope_store(const void* qkv, int64_t qkv_stride_tok,
                           const float* sin_table, int max_position,
                           const void* gamma_q, const void* gamma_k, float eps,
                           void* q_out, void* k_out, void* k_cache,
-                          void* v_cache, const int64_t* slot_mapping,
+                          void* v_cache, void* k_scale, void* v_scale,
+                          const int64_t* slot_mapping,
                           int64_t num_slots, int64_t num_tokens, int num_heads,
                           int num_kv_heads, int head_dim, int dtype,
                           void* stream);

@@ -44,8 +44,8 @@ SIGNATURES = {
                                        _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr]),
     "mv_update_block_tables": (_c_int, [_c_ptr, _c_int, _c_ptr, _c_i64, _c_int, _c_int, _c_ptr]),
     "mv_qk_norm_rope_store": (_c_int, [_c_ptr, _c_i64, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_ptr, _c_ptr, _c_f32,
-                                       _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_i64, _c_i64, _c_int, _c_int,
-                                       _c_int, _c_int, _c_ptr]),
+                                       _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_i64, _c_i64, _c_int,
+                                       _c_int, _c_int, _c_int, _c_ptr]),
     "mv_argmax_rows": (_c_int, [_c_ptr, _c_i64, _c_i64, _c_i64, _c_i64, _c_ptr, _c_ptr, _c_int, _c_ptr]),
     "mv_argmax_decode": (_c_int, [_c_ptr, _c_int, _c_i64, _c_ptr, _c_ptr]),
     "mv_sample_rows": (_c_int, [_c_ptr, _c_i64, _c_i64, _c_i64, _c_i64, _c_ptr, ctypes.c_uint64, _c_ptr, _c_ptr, _c_ptr,

@@ -379,14 +379,12 @@ add_rmsnorm_kernel(void* __restrict__ out_, const void* __restrict__ x_, const v
 template <typename T>
 __global__ void __launch_bounds__(256)
 silu_mul_kernel(void* __restrict__ out_, const void* __restrict__ gu_, int64_t gu_stride, int64_t rows, int inter) {
+  // blockIdx.y walks the rows, blockIdx.x * 256 + threadIdx.x the 16-byte column chunks: no division per element
   const int nvec = inter >> 3;
-  const int64_t total = rows * nvec;
-  uint4* out = reinterpret_cast<uint4*>(out_);
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= nvec) return;
   const T* gu = reinterpret_cast<const T*>(gu_);
-  for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < total;
-       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
-    const int64_t row = i / nvec;
-    const int c = static_cast<int>(i - row * nvec);
+  for (int64_t row = blockIdx.y; row < rows; row += gridDim.y) {
     const T* base = gu + row * gu_stride;
     const uint4 a = ld_stream16(reinterpret_cast<const uint4*>(base) + c);
     const uint4 b = ld_stream16(reinterpret_cast<const uint4*>(base + inter) + c);
@@ -394,8 +392,8 @@ silu_mul_kernel(void* __restrict__ out_, const void* __restrict__ gu_, int64_t g
     Vec8<T>::unpack(a, x);
     Vec8<T>::unpack(b, y);
 #pragma unroll
-    for (int k = 0; k < 8; ++k) r[k] = x[k] / (1.0f + __expf(-x[k])) * y[k];
-    out[i] = Vec8<T>::pack(r);
+    for (int k = 0; k < 8; ++k) r[k] = __fdividef(x[k], 1.0f + __expf(-x[k])) * y[k];
+    reinterpret_cast<uint4*>(out_)[row * nvec + c] = Vec8<T>::pack(r);
   }
 }
 
@@ -710,9 +708,11 @@ extern "C" int mv_silu_mul(void* out, const void* gate_up, int64_t gate_up_strid
     return fail(MV_ERR_SHAPE, "silu_mul: inter (%d) must be a positive multiple of 8 and the row stride a multiple of 8 >= 2*inter", inter);
   if (!aligned16(out) || !aligned16(gate_up)) return fail(MV_ERR_ALIGN, "silu_mul: pointers must be 16-byte aligned");
   if (rows == 0) return MV_OK;
-  const int64_t total = rows * (inter / 8);
-  const int64_t want = (total + 255) / 256;
-  const int grid = static_cast<int>(want < 16 * kNumSMs ? want : 16 * kNumSMs);
+  const int gx = (inter / 8 + 255) / 256;
+  int64_t gy = (16ll * kNumSMs + gx - 1) / gx;          // about 16 resident CTAs per SM in total
+  if (gy > rows) gy = rows;
+  if (gy > 65535) gy = 65535;
+  const dim3 grid(gx, static_cast<unsigned>(gy));
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (dtype == MV_F16) silu_mul_kernel<__half><<<grid, 256, 0, s>>>(out, gate_up, gate_up_stride, rows, inter);
   else if (dtype == MV_BF16) silu_mul_kernel<__nv_bfloat16><<<grid, 256, 0, s>>>(out, gate_up, gate_up_stride, rows, inter);

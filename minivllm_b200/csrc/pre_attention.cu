@@ -16,7 +16,11 @@
 // dtype (as the unfused torch path rounds it), then
 // (x1*cos - x2*sin, x2*cos + x1*sin) in fp32 from the fp32 cos/sin table,
 // rounded once more.  HBM-bound: reads qkv once, writes q, k and the two cache rows.
+// With an int8 cache (kInt8) the k row (after norm and rotation, in the model dtype: the values k_out gets) and
+// the v row are quantised per token and head on their way into the cache, exactly as the quantising
+// store_kvcache does: codes (slots, kv_heads, 128) int8 and fp16 scales (slots, kv_heads).
 #include "common.cuh"
+#include "quant.cuh"
 
 namespace mv {
 
@@ -25,14 +29,35 @@ constexpr int kPreThreads = 256;
 // Eight lanes own one (token, head) row of 128 elements: lane l holds elements
 // 8l..8l+7 and their rotate-half partners 64+8l..64+8l+7 (two 16-byte loads),
 // so a warp works on four rows at once and keeps 1 KB of loads in flight.
+// The eight lanes of a row share its absolute maximum (shuffles among those lanes only: other rows of the warp
+// may be on another branch), every lane derives the scale and quantises its two chunks.
 template <typename T>
+__device__ __forceinline__ void store_row_int8(const uint4& lo, const uint4& hi, int8_t* codes_row, __half* scale_ptr,
+                                               int sub) {
+  const unsigned mask = 0xffu << (threadIdx.x & 24);
+  float amax = fmaxf(chunk_absmax<T>(lo), chunk_absmax<T>(hi));
+  amax = fmaxf(amax, __shfl_xor_sync(mask, amax, 1));
+  amax = fmaxf(amax, __shfl_xor_sync(mask, amax, 2));
+  amax = fmaxf(amax, __shfl_xor_sync(mask, amax, 4));
+  __half scale16;
+  float s, inv;
+  quant_scale(amax, scale16, s, inv);
+  st_global8(codes_row + 8 * sub, quant_codes<T>(lo, s, inv));
+  st_global8(codes_row + 64 + 8 * sub, quant_codes<T>(hi, s, inv));
+  if (sub == 0) *scale_ptr = scale16;
+}
+
+template <typename T, bool kInt8>
 __global__ void __launch_bounds__(kPreThreads)
 qk_norm_rope_store_kernel(const T* __restrict__ qkv, int64_t qkv_stride, const int64_t* __restrict__ positions,
                           const float* __restrict__ cos_tab, const float* __restrict__ sin_tab, int max_position,
                           const T* __restrict__ gamma_q, const T* __restrict__ gamma_k, float eps,
-                          T* __restrict__ q_out, T* __restrict__ k_out, T* __restrict__ k_cache,
-                          T* __restrict__ v_cache, const int64_t* __restrict__ slot_mapping, int64_t num_slots,
-                          int64_t num_tokens, int num_heads, int num_kv_heads) {
+                          T* __restrict__ q_out, T* __restrict__ k_out, void* __restrict__ k_cache_,
+                          void* __restrict__ v_cache_, __half* __restrict__ k_scale, __half* __restrict__ v_scale,
+                          const int64_t* __restrict__ slot_mapping, int64_t num_slots, int64_t num_tokens, int num_heads,
+                          int num_kv_heads) {
+  T* k_cache = static_cast<T*>(k_cache_);
+  T* v_cache = static_cast<T*>(v_cache_);
   constexpr int D = 128;
   using T2 = typename Elem<T>::T2;
   const int sub = threadIdx.x & 7;  // lane within the row group
@@ -75,9 +100,14 @@ qk_norm_rope_store_kernel(const T* __restrict__ qkv, int64_t qkv_stride, const i
     if (!live) continue;
     if (!is_q && !is_k) {  // v: straight copy into the cache
       if (to_cache) {
-        T* dst = v_cache + (slot * num_kv_heads + (h - num_heads - num_kv_heads)) * D;
-        st_global16(dst + 8 * sub, lo);
-        st_global16(dst + 64 + 8 * sub, hi);
+        const int64_t crow = slot * num_kv_heads + (h - num_heads - num_kv_heads);
+        if constexpr (kInt8) {
+          store_row_int8<T>(lo, hi, static_cast<int8_t*>(v_cache_) + crow * D, v_scale + crow, sub);
+        } else {
+          T* dst = v_cache + crow * D;
+          st_global16(dst + 8 * sub, lo);
+          st_global16(dst + 64 + 8 * sub, hi);
+        }
       }
       continue;
     }
@@ -118,9 +148,14 @@ qk_norm_rope_store_kernel(const T* __restrict__ qkv, int64_t qkv_stride, const i
       st_global16(dst + 8 * sub, o_lo);
       st_global16(dst + 64 + 8 * sub, o_hi);
       if (to_cache) {
-        T* cdst = k_cache + (slot * num_kv_heads + kh) * D;
-        st_global16(cdst + 8 * sub, o_lo);
-        st_global16(cdst + 64 + 8 * sub, o_hi);
+        const int64_t crow = slot * num_kv_heads + kh;
+        if constexpr (kInt8) {
+          store_row_int8<T>(o_lo, o_hi, static_cast<int8_t*>(k_cache_) + crow * D, k_scale + crow, sub);
+        } else {
+          T* cdst = k_cache + crow * D;
+          st_global16(cdst + 8 * sub, o_lo);
+          st_global16(cdst + 64 + 8 * sub, o_hi);
+        }
       }
     }
   }
@@ -131,9 +166,9 @@ qk_norm_rope_store_kernel(const T* __restrict__ qkv, int64_t qkv_stride, const i
 extern "C" int mv_qk_norm_rope_store(const void* qkv, int64_t qkv_stride_tok, const int64_t* positions,
                                      const float* cos_table, const float* sin_table, int max_position,
                                      const void* gamma_q, const void* gamma_k, float eps, void* q_out, void* k_out,
-                                     void* k_cache, void* v_cache, const int64_t* slot_mapping, int64_t num_slots,
-                                     int64_t num_tokens, int num_heads, int num_kv_heads, int head_dim, int dtype,
-                                     void* stream) {
+                                     void* k_cache, void* v_cache, void* k_scale, void* v_scale,
+                                     const int64_t* slot_mapping, int64_t num_slots, int64_t num_tokens, int num_heads,
+                                     int num_kv_heads, int head_dim, int dtype, void* stream) {
   using namespace mv;
   if (dtype != MV_F16 && dtype != MV_BF16) return fail(MV_ERR_DTYPE, "qk_norm_rope_store: dtype %d", dtype);
   if (num_tokens < 0 || num_heads <= 0 || num_kv_heads <= 0 || max_position <= 0 || num_slots < 0)
@@ -143,27 +178,32 @@ extern "C" int mv_qk_norm_rope_store(const void* qkv, int64_t qkv_stride_tok, co
   if (!qkv || !positions || !cos_table || !sin_table || !gamma_q || !gamma_k || !q_out || !k_out)
     return fail(MV_ERR_NULL, "qk_norm_rope_store: null pointer");
   if (slot_mapping && (!k_cache || !v_cache)) return fail(MV_ERR_NULL, "qk_norm_rope_store: slot_mapping without caches");
+  if ((k_scale == nullptr) != (v_scale == nullptr))
+    return fail(MV_ERR_NULL, "qk_norm_rope_store: k_scale and v_scale must both be set or both be null");
+  const bool int8 = k_scale != nullptr;
+  if (int8 && !slot_mapping) return fail(MV_ERR_NULL, "qk_norm_rope_store: scales without a slot_mapping");
   const int64_t row = static_cast<int64_t>(num_heads + 2 * num_kv_heads) * head_dim;
   if (qkv_stride_tok < row) return fail(MV_ERR_SHAPE, "qk_norm_rope_store: token stride smaller than a row");
   if (qkv_stride_tok % 8 || !aligned16(qkv) || !aligned16(q_out) || !aligned16(k_out) || !aligned16(cos_table) ||
       !aligned16(sin_table) || !aligned16(gamma_q) || !aligned16(gamma_k) || (k_cache && !aligned16(k_cache)) ||
-      (v_cache && !aligned16(v_cache)))
+      (v_cache && !aligned16(v_cache)) || (int8 && (!aligned16(k_scale) || !aligned16(v_scale))))
     return fail(MV_ERR_ALIGN, "qk_norm_rope_store: misaligned pointer or stride");
   const int64_t rows = num_tokens * (num_heads + 2 * num_kv_heads);
   int64_t grid = (rows + kPreThreads / 8 - 1) / (kPreThreads / 8);
   if (grid > static_cast<int64_t>(kNumSMs) * 8) grid = static_cast<int64_t>(kNumSMs) * 8;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  if (dtype == MV_F16)
-    qk_norm_rope_store_kernel<__half><<<static_cast<int>(grid), kPreThreads, 0, st>>>(
-        static_cast<const __half*>(qkv), qkv_stride_tok, positions, cos_table, sin_table, max_position,
-        static_cast<const __half*>(gamma_q), static_cast<const __half*>(gamma_k), eps, static_cast<__half*>(q_out),
-        static_cast<__half*>(k_out), static_cast<__half*>(k_cache), static_cast<__half*>(v_cache), slot_mapping,
-        num_slots, num_tokens, num_heads, num_kv_heads);
-  else
-    qk_norm_rope_store_kernel<__nv_bfloat16><<<static_cast<int>(grid), kPreThreads, 0, st>>>(
-        static_cast<const __nv_bfloat16*>(qkv), qkv_stride_tok, positions, cos_table, sin_table, max_position,
-        static_cast<const __nv_bfloat16*>(gamma_q), static_cast<const __nv_bfloat16*>(gamma_k), eps,
-        static_cast<__nv_bfloat16*>(q_out), static_cast<__nv_bfloat16*>(k_out), static_cast<__nv_bfloat16*>(k_cache),
-        static_cast<__nv_bfloat16*>(v_cache), slot_mapping, num_slots, num_tokens, num_heads, num_kv_heads);
+  __half* ks = static_cast<__half*>(k_scale);
+  __half* vs = static_cast<__half*>(v_scale);
+#define MV_PRE_LAUNCH(T, I8)                                                                                          \
+  qk_norm_rope_store_kernel<T, I8><<<static_cast<int>(grid), kPreThreads, 0, st>>>(                                    \
+      static_cast<const T*>(qkv), qkv_stride_tok, positions, cos_table, sin_table, max_position,                       \
+      static_cast<const T*>(gamma_q), static_cast<const T*>(gamma_k), eps, static_cast<T*>(q_out), static_cast<T*>(k_out), \
+      k_cache, v_cache, ks, vs, slot_mapping, num_slots, num_tokens, num_heads, num_kv_heads)
+  if (dtype == MV_F16) {
+    if (int8) MV_PRE_LAUNCH(__half, true); else MV_PRE_LAUNCH(__half, false);
+  } else {
+    if (int8) MV_PRE_LAUNCH(__nv_bfloat16, true); else MV_PRE_LAUNCH(__nv_bfloat16, false);
+  }
+#undef MV_PRE_LAUNCH
   return check_launch("qk_norm_rope_store_kernel");
 }

@@ -48,6 +48,11 @@ class ModelRunner:
         self.dtype = config.get("dtype", torch.bfloat16)
         self.device = torch.device(device if device is not None else f"cuda:{torch.cuda.current_device()}")
         self.greedy = config.get("greedy", False)
+        # "int8": per-token-per-head symmetric int8 KV cache with fp16 scales (no counterpart in the reference)
+        self.kv_int8 = config.get("kv_cache_dtype", None) == "int8"
+        if self.kv_int8 and config.get("enable_prefix_caching", False):
+            raise ValueError("kv_cache_dtype='int8' cannot be combined with prefix caching: the prefix-aware prefill "
+                             "kernel reads fp16/bf16 caches only")
         mcfg = Qwen3Config.from_dict(config)
         mcfg.max_position = max(mcfg.max_position, self.max_model_len)
         self.model_cfg = mcfg
@@ -78,8 +83,10 @@ class ModelRunner:
     # ------------------------------------------------------------------ memory ---
     def kv_block_bytes(self):
         c = self.model_cfg
-        return self.block_size * 2 * c.num_layers * (c.num_kv_heads // self.world_size) * c.head_dim * \
-            torch.empty((), dtype=self.dtype).element_size()
+        rows = self.block_size * 2 * c.num_layers * (c.num_kv_heads // self.world_size)
+        if self.kv_int8:
+            return rows * (c.head_dim + 2)             # int8 codes + one fp16 scale per row
+        return rows * c.head_dim * torch.empty((), dtype=self.dtype).element_size()
 
     def allocate_kv_cache(self):
         """One pool (2, layers, blocks, block_size, kv_heads/tp, head_dim); every module that has
@@ -99,13 +106,18 @@ class ModelRunner:
                 num_blocks = int(t.item())
         assert num_blocks >= 1, f"not enough memory for one KV block on rank {self.rank}"
         self.num_kv_blocks = num_blocks
-        self.kv_cache = torch.zeros(2, c.num_layers, num_blocks, self.block_size, c.num_kv_heads // self.world_size,
-                                    c.head_dim, dtype=self.dtype, device=self.device)
+        kvh = c.num_kv_heads // self.world_size
+        self.kv_cache = torch.zeros(2, c.num_layers, num_blocks, self.block_size, kvh, c.head_dim,
+                                    dtype=torch.int8 if self.kv_int8 else self.dtype, device=self.device)
+        self.kv_scale = torch.zeros(2, c.num_layers, num_blocks, self.block_size, kvh, dtype=torch.float16,
+                                    device=self.device) if self.kv_int8 else None
         layer = 0
         for module in self.model.modules():
             if hasattr(module, "k_cache") and hasattr(module, "v_cache"):
                 module.k_cache = self.kv_cache[0, layer]
                 module.v_cache = self.kv_cache[1, layer]
+                if self.kv_int8:
+                    module.k_scale, module.v_scale = self.kv_scale[0, layer], self.kv_scale[1, layer]
                 layer += 1
         assert layer == c.num_layers
 

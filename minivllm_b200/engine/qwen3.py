@@ -155,7 +155,8 @@ class DecoderLayer(nn.Module):
             ctx = get_context()
             a = self.attn
             q, k = qk_norm_rope_store(qkv, ctx.positions, rope[0], rope[1], self.qk_norm_w, self.qk_norm_w, RMS_EPS,
-                                      self.h, self.kvh, self.d, a.k_cache, a.v_cache, ctx.slot_mapping)
+                                      self.h, self.kvh, self.d, a.k_cache, a.v_cache, ctx.slot_mapping,
+                                      k_scale=a.k_scale, v_scale=a.v_scale)
             return a(q, k, v, store=False)
         # the reference's separate steps (src/myvllm/models/qwen3.py:104-110); the attention module stores K/V
         q, k, _ = qkv.split([self.h * self.d, self.kvh * self.d, self.kvh * self.d], dim=-1)

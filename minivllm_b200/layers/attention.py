@@ -240,14 +240,16 @@ def flash_attention_prefill_paged(q, k_cache, v_cache, cu_seqlens_q, cu_seqlens_
 
 
 def qk_norm_rope_store(qkv, positions, cos_table, sin_table, gamma_q, gamma_k, eps, num_heads, num_kv_heads,
-                       head_dim, k_cache=None, v_cache=None, slot_mapping=None):
+                       head_dim, k_cache=None, v_cache=None, slot_mapping=None, k_scale=None, v_scale=None):
     """One launch for what the reference does in a dozen before attention: RMSNorm of the q and k heads,
     rotary embedding, and the scatter of k and v into the paged cache.
 
     qkv (tokens, (heads + 2*kv_heads) * head_dim) is the fused projection output (any token stride);
     positions (tokens,) int64; cos_table / sin_table (max_position, head_dim/2) fp32.
     Returns (q, k) as new contiguous (tokens, heads, head_dim) / (tokens, kv_heads, head_dim) tensors; v is
-    still `qkv[..., -kv_heads*head_dim:]`.  With caches and a slot_mapping, k and v are also stored.
+    still `qkv[..., -kv_heads*head_dim:]`.  With caches and a slot_mapping, k and v are also stored; with
+    `k_scale` / `v_scale` (fp16, (blocks, block_size, kv_heads)) the caches are int8 and the rows are quantised on
+    the way in, exactly as `store_kvcache(k, v, ..., k_scale=, v_scale=)` would.
     Reference: src/myvllm/models/qwen3.py:104-108 and src/myvllm/layers/attention.py:498-510.
     """
     _cabi.require_cuda(qkv, positions, cos_table, sin_table, gamma_q, gamma_k)
@@ -263,15 +265,26 @@ def qk_norm_rope_store(qkv, positions, cos_table, sin_table, gamma_q, gamma_k, e
     q = torch.empty((tokens, num_heads, head_dim), dtype=qkv.dtype, device=qkv.device)
     k = torch.empty((tokens, num_kv_heads, head_dim), dtype=qkv.dtype, device=qkv.device)
     store = slot_mapping is not None and k_cache is not None and k_cache.numel() > 0
+    quant = k_scale is not None or v_scale is not None
+    if quant and (k_scale is None or v_scale is None or not store):
+        raise ValueError("k_scale and v_scale must be given together, with caches and a slot_mapping")
     if store:
-        if k_cache.dtype != qkv.dtype or v_cache.dtype != qkv.dtype or tuple(k_cache.shape[2:]) != (num_kv_heads, head_dim):
-            raise ValueError("fused store needs fp16/bf16 caches of shape (blocks, block_size, kv_heads, head_dim)")
+        want = torch.int8 if quant else qkv.dtype
+        if k_cache.dtype != want or v_cache.dtype != want or tuple(k_cache.shape[2:]) != (num_kv_heads, head_dim) or \
+                not (k_cache.is_contiguous() and v_cache.is_contiguous()):
+            raise ValueError("fused store needs contiguous caches (blocks, block_size, kv_heads, head_dim) of the model "
+                             "dtype, or int8 caches together with scales")
+        if quant:
+            for sc in (k_scale, v_scale):
+                if sc.dtype != torch.float16 or tuple(sc.shape) != tuple(k_cache.shape[:3]) or not sc.is_contiguous():
+                    raise ValueError("scales must be contiguous fp16 tensors of shape (blocks, block_size, kv_heads)")
         if slot_mapping.dtype != torch.int64 or slot_mapping.numel() != tokens:
             raise ValueError("slot_mapping must be int64 with one entry per token")
     rc = _cabi.lib().mv_qk_norm_rope_store(
         qkv.data_ptr(), qkv.stride(0) if tokens > 1 else width, positions.data_ptr(), cos_table.data_ptr(),
         sin_table.data_ptr(), cos_table.shape[0], gamma_q.data_ptr(), gamma_k.data_ptr(), float(eps), q.data_ptr(),
         k.data_ptr(), k_cache.data_ptr() if store else None, v_cache.data_ptr() if store else None,
+        k_scale.data_ptr() if quant else None, v_scale.data_ptr() if quant else None,
         slot_mapping.data_ptr() if store else None, k_cache.shape[0] * k_cache.shape[1] if store else 0, tokens,
         num_heads, num_kv_heads, head_dim, _cabi.dtype_code(qkv.dtype), _cabi.stream_ptr())
     _cabi.check(rc)

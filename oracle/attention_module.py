@@ -16,14 +16,22 @@ class OracleAttention(nn.Module):
         self.num_kv_heads = num_kv_heads if num_kv_heads is not None else num_heads
         self.block_size = block_size
         self.k_cache = self.v_cache = torch.tensor([])
+        self.k_scale = self.v_scale = None      # set: int8 caches (codes) with fp16 scales
 
     def forward(self, q, k, v, store=True):
         ctx = get_context()
         dev, dt = q.device, q.dtype
         kc, vc = self.k_cache, self.v_cache
+        int8 = self.k_scale is not None
         if kc.numel() > 0 and ctx.slot_mapping is not None:
             kcc, vcc = kc.cpu(), vc.cpu()
-            oracle.store_kvcache(k.cpu(), v.cpu(), kcc, vcc, ctx.slot_mapping.cpu())
+            if int8:
+                ksc, vsc = self.k_scale.cpu(), self.v_scale.cpu()
+                oracle.store_kvcache_int8(k.cpu(), v.cpu(), kcc, vcc, ksc, vsc, ctx.slot_mapping.cpu())
+                self.k_scale.copy_(ksc)
+                self.v_scale.copy_(vsc)
+            else:
+                oracle.store_kvcache(k.cpu(), v.cpu(), kcc, vcc, ctx.slot_mapping.cpu())
             kc.copy_(kcc)
             vc.copy_(vcc)
         scale = self.scale / self.head_dim ** 0.5
@@ -31,7 +39,11 @@ class OracleAttention(nn.Module):
             o = oracle.flash_attention_prefill(q.cpu(), k.cpu(), v.cpu(), ctx.cu_seqlens_q.cpu(), scale,
                                                self.num_heads, self.num_kv_heads, self.head_dim)
         else:
-            o = oracle.paged_attention_decode(q.cpu(), kc.cpu(), vc.cpu(), ctx.block_tables.cpu(),
+            kf, vf = kc.cpu(), vc.cpu()
+            if int8:      # the decode kernel's contract: attention over float(code) * float(scale)
+                kf = oracle.dequantize_kv_int8(kf, self.k_scale.cpu())
+                vf = oracle.dequantize_kv_int8(vf, self.v_scale.cpu())
+            o = oracle.paged_attention_decode(q.cpu(), kf, vf, ctx.block_tables.cpu(),
                                               ctx.context_lens.cpu(), scale, self.num_heads, self.num_kv_heads,
                                               self.head_dim, kc.shape[1])
         return o.to(dt).to(dev).reshape(o.shape[0], self.num_heads * self.head_dim)
@@ -43,6 +55,7 @@ def swap_in_oracle_attention(model):
         a = layer.attn
         o = OracleAttention(a.num_heads, a.head_dim, a.scale, a.num_kv_heads, a.block_size)
         o.k_cache, o.v_cache = a.k_cache, a.v_cache
+        o.k_scale, o.v_scale = getattr(a, "k_scale", None), getattr(a, "v_scale", None)
         layer.attn = o
         layer.fused_pre_attention = False   # the reference path: separate norm, RoPE and store
     return model

@@ -74,3 +74,44 @@ def test_fused_norm_rope_store_on_gpu(dtype):
     q3, k3 = A.qk_norm_rope_store(qkv.to(dev), pos.to(dev), cos.to(dev), sin.to(dev), gq.to(dev), gk.to(dev), 1e-5,
                                   H, KVH, D)
     assert torch.equal(q3, q) and torch.equal(k3, k)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_fused_norm_rope_store_into_an_int8_cache(dtype):
+    """The int8 variant of the fusion: codes and fp16 scales in the cache equal, bit for bit, what the quantising
+    store_kvcache writes for the kernel's own k output and the raw v (which is itself bit-exact against the
+    CPU definition, tests/test_store_kvcache_gpu.py), and therefore equal the CPU quantiser applied to them."""
+    from minivllm_b200.layers import attention as A
+    dev = "cuda:0"
+    g = torch.Generator().manual_seed(43)
+    tokens, H, KVH, D, bs, nb = 257, 4, 2, 128, 16, 24
+    qkv = (torch.randn(tokens, (H + 2 * KVH) * D, generator=g) * 2).to(dtype)
+    qkv[5, H * D:(H + 1) * D] = 0                      # an all-zero k row: scale 0, codes 0
+    qkv[7, (H + KVH) * D + 3] = 60000.0 if dtype == torch.float16 else 3e38   # a huge v element
+    gam = (torch.rand(D, generator=g) + 0.5).to(dtype)
+    pos = torch.randint(0, 2000, (tokens,), generator=g)
+    inv = 1.0 / (1e6 ** (torch.arange(0, D, 2).float() / D))
+    ang = torch.arange(2048).float()[:, None] * inv[None, :]
+    cos, sin = torch.cos(ang).to(dev), torch.sin(ang).to(dev)
+    slots = torch.randperm(nb * bs, generator=g)[:tokens]
+    slots[torch.rand(tokens, generator=g) < 0.1] = -1
+    mk = lambda: (torch.full((nb, bs, KVH, D), 7, dtype=torch.int8, device=dev),
+                  torch.full((nb, bs, KVH), 3.0, dtype=torch.float16, device=dev))
+    (kq, ks), (vq, vs) = mk(), mk()
+    q, k = A.qk_norm_rope_store(qkv.to(dev), pos.to(dev), cos, sin, gam.to(dev), gam.to(dev), 1e-5, H, KVH, D, kq, vq,
+                                slots.to(dev), k_scale=ks, v_scale=vs)
+    (kq2, ks2), (vq2, vs2) = mk(), mk()
+    v_in = qkv[:, (H + KVH) * D:].reshape(tokens, KVH, D).to(dev)
+    A.store_kvcache(k, v_in, kq2, vq2, slots.to(dev), bs, k_scale=ks2, v_scale=vs2)
+    torch.cuda.synchronize()
+    assert torch.equal(kq, kq2) and torch.equal(vq, vq2) and torch.equal(ks, ks2) and torch.equal(vs, vs2)
+    live = slots >= 0
+    codes, scales = oracle.quantize_kv_int8(k.cpu()[live])
+    assert torch.equal(kq.cpu().view(-1, KVH, D)[slots[live]], codes)
+    assert torch.equal(ks.cpu().view(-1, KVH)[slots[live]], scales)
+    # the same q and k as the unquantised call
+    kc, vc = (torch.zeros(nb, bs, KVH, D, dtype=dtype, device=dev) for _ in range(2))
+    q2, k2 = A.qk_norm_rope_store(qkv.to(dev), pos.to(dev), cos, sin, gam.to(dev), gam.to(dev), 1e-5, H, KVH, D, kc, vc,
+                                  slots.to(dev))
+    assert torch.equal(q, q2) and torch.equal(k, k2)
