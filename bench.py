@@ -542,17 +542,17 @@ class EngineWorkload:
         return (self.out_tokens_per_step) * 8
 
     def launches_per_step(self):
-        """Kernels of this library launched by one generate(): per model step and layer one store_kvcache and
-        one attention call (decode = split-K kernel + combine), plus the metadata kernels of the step and its
-        greedy sampling tail (row argmax; under tensor parallelism also the key decode after the all-reduce)."""
+        """Kernels of this library launched by one generate() (counted from the code path, see below), plus the
+        metadata kernels of the step and its greedy sampling tail (row argmax; under tensor parallelism also the
+        key decode after the all-reduce)."""
         s = self.last_stats
         layers = self.cfg["num_layers"]
         decode_steps = self.out_tokens_per_step // len(self.prompts) - 1
         prefill_waves = s["steps"] - decode_steps
         tail = (2 if self.world > 1 else 1) if self.cfg.get("greedy", False) else 0
-        # per layer: fused q/k norm + RoPE + store, attention (decode: split-K + combine), two fused
-        # (all-reduce +) add + norm kernels, SwiGLU activation; per step: the first norm and the metadata kernel
-        return decode_steps * (layers * 6 + 2 + tail) + prefill_waves * (layers * 5 + 3 + tail)
+        # per layer: fused q/k norm + RoPE + store, attention (one launch in decode and in prefill), two fused
+        # (all-reduce +) add + norm kernels, SwiGLU activation; per step: the first norm and the metadata kernel(s)
+        return decode_steps * (layers * 5 + 2 + tail) + prefill_waves * (layers * 5 + 3 + tail)
 
     def decode_probe(self, iters=36):
         """Times paged_attention_decode with CUDA events on the engine's own KV pool at the shape of the
