@@ -145,3 +145,29 @@ def test_prefix_cache_reuses_full_blocks_but_never_the_last_one():
     f = Sequence([7, 7, 7, 1, 2, 3], block_size=4)
     bm.allocate(f)
     assert f.num_cached_tokens == 4 and f.block_table[0] == e.block_table[0]
+
+
+def test_scheduler_lookahead_bookkeeping_without_token_values():
+    """advance() is postprocess() with the tokens still on the GPU: lengths grow, sequences finish by count,
+    blocks are released; fill_tokens() patches the values in afterwards, also into finished sequences."""
+    sch = Scheduler(max_num_seqs=4, max_num_batched_tokens=100, num_blocks=8, block_size=4, eos=-1)
+    a = Sequence([1, 2, 3], SamplingParams(max_tokens=2, ignore_eos=True), block_size=4)
+    b = Sequence([4, 5, 6, 7, 8], SamplingParams(max_tokens=1, ignore_eos=True), block_size=4)
+    sch.add_sequence(a); sch.add_sequence(b)
+    seqs, is_prefill = sch.schedule()
+    assert is_prefill and sch.can_run_ahead(seqs) and sch.no_preemption_next()
+    at = sch.advance(seqs)
+    assert at == [3, 5] and b.is_finished and not a.is_finished and len(a) == 4
+    nxt, is_prefill = sch.schedule()                      # the next step is schedulable before the tokens arrive
+    assert not is_prefill and nxt == [a]
+    at2 = sch.advance(nxt)
+    assert a.is_finished and sch.is_finished()
+    sch.fill_tokens(seqs, at, [10, 11])
+    sch.fill_tokens(nxt, at2, [12])
+    assert a.completion_token_ids == [10, 12] and b.completion_token_ids == [11]
+    # a sequence that may stop on EOS cannot be run ahead of, nor can anything with the prefix cache on
+    sch2 = Scheduler(max_num_seqs=2, max_num_batched_tokens=100, num_blocks=8, block_size=4, eos=7)
+    c = Sequence([1, 2], SamplingParams(max_tokens=4, ignore_eos=False), block_size=4)
+    assert not sch2.can_run_ahead([c])
+    sch3 = Scheduler(max_num_seqs=2, max_num_batched_tokens=100, num_blocks=8, block_size=4, eos=-1, prefix_caching=True)
+    assert not sch3.can_run_ahead([a])
