@@ -59,6 +59,33 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
     if (mbar_try_wait(bar, parity)) return true;
   return mbar_wait_slow(bar, parity, abort_flag, error_word, where);
 }
+// The same wait in as little code as possible, for a kernel whose MMA-issuing warp has a dozen waits in its loop:
+// that warp shares an instruction cache with the (large) softmax loop, and with the spin loops unrolled its code
+// is pushed out of the cache at every unit boundary (measured: 0.61 ms against 0.51 ms on the 32-sequence
+// benchmark).  The part that runs when a wait is long is a call.
+__device__ __noinline__ bool mbar_wait_long(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* error_word,
+                                            int where) {
+  const unsigned long long t0 = global_ns();
+  for (;;) {
+#pragma unroll 1
+    for (int i = 0; i < 256; ++i)
+      if (mbar_try_wait(bar, parity)) return true;
+    if (*abort_flag) return false;
+    if (global_ns() - t0 > kWaitLimitNs) break;
+  }
+  *abort_flag = 1;
+  atomicCAS(error_word, 0, 0x100 + where);
+  return false;
+}
+template <bool kCall>
+__device__ __forceinline__ bool mbar_wait_compact(uint32_t bar, uint32_t parity, volatile int* abort_flag,
+                                                  int* error_word, int where) {
+#pragma unroll 1
+  for (int i = 0; i < 64; ++i)
+    if (mbar_try_wait(bar, parity)) return true;
+  if (kCall) return mbar_wait_long(bar, parity, abort_flag, error_word, where);
+  return mbar_wait_slow(bar, parity, abort_flag, error_word, where);
+}
 // Wait bounded by time alone (2 ms), for draining copies in flight after an abort.
 __device__ __forceinline__ bool mbar_wait_timed(uint32_t bar, uint32_t parity) {
   const unsigned long long t0 = global_ns();

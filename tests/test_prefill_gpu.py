@@ -187,3 +187,24 @@ def test_prefill_benchmark_configuration_exactly():
     d = synth.prefill_inputs()                      # the defaults ARE that configuration (seed 1)
     assert d["q"].shape[0] == 34277 and d["num_heads"] == 32 and d["num_kv_heads"] == 8
     _close(_gpu(d, torch.bfloat16), _oracle(d, torch.bfloat16), torch.bfloat16)
+
+
+@pytest.mark.parametrize("form", [1, 2])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_prefill_both_launch_forms(form, dtype):
+    """One CTA per query tile (form 1) and persistent CTAs that stream through their tiles (form 2): the launch
+    picks by the number of sequences; here each is forced in turn (measurement hook outside the public header)
+    on ragged batches -- more units than SMs, odd and single-head groups, a one-tile batch -- and must match
+    the oracle."""
+    lib = _cabi.lib()
+    try:
+        assert lib.mv_debug_prefill_form(ctypes.c_int(form)) == 0
+        for kw in (dict(num_seqs=9, len_lo=1, len_hi=900, num_heads=8, num_kv_heads=2),
+                   dict(num_seqs=14, len_lo=250, len_hi=900, num_heads=6, num_kv_heads=2),
+                   dict(num_seqs=2, len_lo=129, len_hi=400, num_heads=3, num_kv_heads=3),
+                   dict(num_seqs=1, len_lo=17, len_hi=17, num_heads=2, num_kv_heads=1),
+                   dict(num_seqs=300, len_lo=0, len_hi=90, num_heads=4, num_kv_heads=2)):
+            d = synth.prefill_inputs(seed=66, head_dim=128, **kw)
+            _close(_gpu(d, dtype), _oracle(d, dtype), dtype)
+    finally:
+        lib.mv_debug_prefill_form(ctypes.c_int(0))
