@@ -512,6 +512,10 @@ class EngineWorkload:
         self.rank, self.world, self.device = rank, world, device
         if os.environ.get("MV_CUSTOM_ALLREDUCE", "1") == "0":      # A/B switch: the NCCL all-reduce path
             cfg_over.setdefault("custom_allreduce", False)
+        if os.environ.get("MV_PREFILL_STREAMS"):                   # A/B switch: 1 = one prefill wave at a time
+            cfg_over.setdefault("prefill_streams", int(os.environ["MV_PREFILL_STREAMS"]))
+        if os.environ.get("MV_PREFILL_COMM_BLOCKS"):               # grid cap of the all-reduce beside another wave
+            cfg_over.setdefault("prefill_comm_blocks", int(os.environ["MV_PREFILL_COMM_BLOCKS"]))
         self.cfg = configs.qwen3_8b_config(world_size=world, **cfg_over)
         self.prompts, self.sp = configs.qwen3_8b_requests(n=requests, new_tokens=new_tokens)
         self.engine = LLMEngine(self.cfg, rank=rank, world_size=world)
@@ -985,6 +989,33 @@ def run_allreduce(args, rank, world, local, device, dist_on, pk):
         res["frac_of_measured_peer_copy_770GBps"] = res["link_GBps_per_direction"] / link_gbs
         res["speedup_vs_nccl_torch"] = res["nccl_plus_torch_add_norm_us"] / res["fused_kernel_us"]
         out[label] = res
+    # The same kernel over the row counts between the two: launched one by one, replayed from a CUDA graph of 20
+    # launches (no launch gaps, as in the engine's decode graph), and the NCCL all-reduce alone for comparison.
+    sweep = {}
+    for rows in (1, 64, 256, 512, 1024, 4096, 16384):
+        lo, hi = shard_rows(rows, rank, world)
+        shard = torch.zeros(max(hi - lo, 1), hidden, dtype=dt, device=device)
+        x = torch.zeros(rows, hidden, dtype=dt, device=device)
+        iters = 200 if rows <= 4096 else 40
+        comm.input_rows(rows).zero_()
+
+        def fused(rows=rows, shard=shard):
+            comm.allreduce_residual_rmsnorm(rows, shard, gamma, 1e-5)
+
+        eager_ms, _, _ = device_timed(lambda: [fused() for _ in range(iters)], 1, 3, dist_on)
+        graph, side = torch.cuda.CUDAGraph(), torch.cuda.Stream()
+        with torch.cuda.stream(side):
+            with torch.cuda.graph(graph, stream=side):
+                for _ in range(20):
+                    fused()
+        graph_ms, _, _ = device_timed(lambda: [graph.replay() for _ in range(10)], 1, 3, dist_on)
+        nccl_ms, _, _ = device_timed(lambda: [dist.all_reduce(x) for _ in range(iters // 2)], 1, 3, dist_on)
+        sweep[str(rows)] = {"fused_us": eager_ms * 1e3 / iters, "fused_in_graph_us": graph_ms * 1e3 / 200,
+                            "nccl_allreduce_only_us": nccl_ms * 1e3 / (iters // 2)}
+        del graph
+    torch.cuda.synchronize()
+    assert int(comm.error_word.item()) == 0, "an all-reduce wait ran out of time"
+    out["rows_sweep"] = sweep
     d = out["decode_512rows"]
     line = {"metric": "all-reduce + residual + RMSNorm latency (512 rows x 4096 bf16)", "value": d["fused_kernel_us"],
             "unit": "us", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,

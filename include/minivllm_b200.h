@@ -365,6 +365,10 @@ int mv_comm_create_emulated(int world, int64_t data_bytes, int timeout_ms,
                             void** comm_out);
 int mv_comm_destroy(void* comm);
 int mv_comm_reset(void* comm);
+/* Caps the grid of the following mv_allreduce_residual_rmsnorm launches of this communicator (0 = no cap).  A
+ * block of that kernel occupies a whole SM; a caller that keeps a second stream busy with GEMMs while a
+ * bandwidth-bound call runs leaves them the remaining SMs this way.  Results do not depend on the grid. */
+int mv_comm_set_max_blocks(void* comm, int max_blocks);
 void* mv_comm_input(void* comm, int slot);
 void* mv_comm_output(void* comm, int slot);
 int mv_allreduce_residual_rmsnorm(void* comm, void* residual_shard,

@@ -57,6 +57,7 @@ SIGNATURES = {
     "mv_comm_create_emulated": (_c_int, [_c_int, _c_i64, _c_int, ctypes.POINTER(_c_ptr)]),
     "mv_comm_destroy": (_c_int, [_c_ptr]),
     "mv_comm_reset": (_c_int, [_c_ptr]),
+    "mv_comm_set_max_blocks": (_c_int, [_c_ptr, _c_int]),
     "mv_comm_input": (_c_ptr, [_c_ptr, _c_int]),
     "mv_comm_output": (_c_ptr, [_c_ptr, _c_int]),
     "mv_allreduce_residual_rmsnorm": (_c_int, [_c_ptr, _c_ptr, _c_i64, _c_ptr, _c_f32, _c_int, _c_int, _c_ptr,

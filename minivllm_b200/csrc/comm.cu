@@ -77,6 +77,7 @@ struct Comm {
   CommSlot* table_dev = nullptr;      // inside region[rank] (region[0] in emulation)
   unsigned long long timeout_ns = 0;
   int device = 0;
+  int max_blocks = 0;                 // 0 = as many as the rows want; else a cap (mv_comm_set_max_blocks)
 };
 
 // Control region layout (byte offsets inside a rank's region).
@@ -577,6 +578,17 @@ extern "C" int mv_comm_reset(void* comm) {
   return write_table(c);
 }
 
+// Caps the grid of the following launches (0 = no cap).  A block of this kernel takes a whole SM; a caller that
+// runs another stream's GEMMs beside a bandwidth-bound all-reduce (two prefill waves in flight) leaves them the
+// other SMs this way.  Any grid size is valid: rows are strided over blocks and the barriers do not depend on it.
+extern "C" int mv_comm_set_max_blocks(void* comm, int max_blocks) {
+  Comm* c = static_cast<Comm*>(comm);
+  if (!c) return fail(MV_ERR_NULL, "comm_set_max_blocks: null communicator");
+  if (max_blocks < 0) return fail(MV_ERR_SHAPE, "comm_set_max_blocks: negative cap");
+  c->max_blocks = max_blocks;
+  return MV_OK;
+}
+
 // Test hook (not in the public header): the next launches of `slot` withhold their first-barrier signal, so
 // the other ranks' bounded waits run out and report through the error word.  Cleared by mv_comm_reset.
 extern "C" int mv_debug_comm_withhold_signal(void* comm, int slot) {
@@ -613,6 +625,7 @@ static int launch_allreduce(Comm* c, void* residual, int64_t residual_slot_strid
   const int rows_per = (rows + c->world - 1) / c->world;
   int at_once = comm_rows_at_once(rows_per, c->world, vpt, threads);
   int blocks = comm_grid(rows_per, at_once, threads);
+  if (c->max_blocks > 0 && blocks > c->max_blocks) blocks = c->max_blocks;
   if (c->emulated) {            // all ranks share one GPU: one row at a time, and few enough blocks to be co-resident
     at_once = 1;
     blocks = comm_grid(rows_per, 1, threads);

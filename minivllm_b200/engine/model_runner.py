@@ -62,6 +62,19 @@ class ModelRunner:
         self.comm, self.comm_note = None, "single rank"
         if self.world_size > 1:
             self._attach_communicator()
+        # prefill_streams=2: two prefill waves in flight on two streams, each with a communicator of its own, so
+        # that one wave's all-reduces (NVLink-bound, a capped number of SMs) can run beside the other wave's GEMMs.
+        # Off by default: the all-reduce kernel keeps one row group in flight per block and needs most SMs to
+        # fill the link (16,384 rows on 2 GPUs: 220 us on 296 blocks, 486 us on 48), so the overlap gains
+        # nothing yet.  Greedy runs only: a sampled run advances one step counter in stream order.
+        self.prefill_lanes, self._prefill_at = [], 0
+        want = int(config.get("prefill_streams", 1))
+        if want >= 2 and self.greedy and self.device.type == "cuda":
+            second = self._new_communicator() if self.comm is not None else None
+            if self.comm is None or second is not None:
+                self.prefill_lanes = [(torch.cuda.Stream(device=self.device), self.comm),
+                                      (torch.cuda.Stream(device=self.device), second)]
+        self.prefill_comm_blocks = int(config.get("prefill_comm_blocks", 48))
         self.error_word = _error_word(self.device)
         self.max_blocks_per_seq = math.ceil(self.max_model_len / self.block_size)
         # one spare slot: padded rows of a captured batch point at it
@@ -167,6 +180,17 @@ class ModelRunner:
         if not self.config.get("custom_allreduce", True):
             self.comm_note = "NCCL all-reduce (custom_allreduce=False)"
             return
+        comm = self._new_communicator()
+        if comm is not None:
+            self.comm, self.model.comm = comm, comm
+            self.comm_note = "fused all-reduce + residual + RMSNorm kernel over NVLink peer memory"
+        else:
+            self.comm_note = "NCCL all-reduce (peer-memory communicator unavailable: %s)" % self._comm_error
+            if self.rank == 0:
+                print("minivllm_b200: " + self.comm_note, flush=True)
+
+    def _new_communicator(self):
+        """A peer-memory communicator for this rank, or None on EVERY rank if any rank could not set it up."""
         from ..layers.allreduce import TPCommunicator
         err, comm = "", None
         try:
@@ -177,14 +201,11 @@ class ModelRunner:
         ok = torch.tensor([0 if err else 1], device=self.device, dtype=torch.int32)
         dist.all_reduce(ok, op=dist.ReduceOp.MIN)
         if int(ok.item()) == 1:
-            self.comm, self.model.comm = comm, comm
-            self.comm_note = "fused all-reduce + residual + RMSNorm kernel over NVLink peer memory"
-        else:
-            if comm is not None:
-                comm.close()
-            self.comm_note = "NCCL all-reduce (peer-memory communicator unavailable: %s)" % (err or "failed on another rank")
-            if self.rank == 0:
-                print("minivllm_b200: " + self.comm_note, flush=True)
+            return comm
+        if comm is not None:
+            comm.close()
+        self._comm_error = err or "failed on another rank"
+        return None
 
     def _upload_slots(self, seqs, slots_buf, n_active_buf):
         """Slot ids of the batch (padding rows point at the spare slot) and the live count: one pinned staging
@@ -257,18 +278,18 @@ class ModelRunner:
     def launch(self, seqs, is_prefill):
         """Enqueues one model step and the device->host copy of its result; returns a handle for `finish`.
         Nothing here waits for the GPU."""
+        if is_prefill and self.prefill_lanes:
+            return self._launch_prefill_lane(seqs)
+        main = torch.cuda.current_stream() if self.device.type == "cuda" else None
+        for stream, _ in self.prefill_lanes:         # a step on the main stream sees every wave launched so far
+            main.wait_stream(stream)
         temps = None
         if not self.greedy:
             temps = torch.tensor([s.temperature for s in seqs], dtype=torch.float32).pin_memory().to(
                 self.device, non_blocking=True)
         n = len(seqs)
         if is_prefill:
-            input_ids = self.prepare_prefill(seqs)
-            tokens = self.next_tokens(self.run_model(input_ids, True), temps)
-            slots = torch.tensor([s.slot for s in seqs], dtype=torch.int64).pin_memory().to(self.device,
-                                                                                             non_blocking=True)
-            self.state.last_token.index_copy_(0, slots, tokens)
-            result = torch.cat([tokens, self.error_word.to(torch.int64)])
+            result = self._prefill_body(seqs, temps)
         elif self.enforce_eager or not self.graphs:
             input_ids, slots_buf = self.prepare_decode(seqs)
             tokens = self.next_tokens(self.run_model(input_ids, False), temps)
@@ -280,12 +301,53 @@ class ModelRunner:
         if self._readback is None:
             self._readback = [torch.empty(max(self.max_num_seqs, self.max_num_batched_tokens) + 1,
                                           dtype=torch.int64).pin_memory() for _ in range(4)]
+        return self._read_back(result, n)
+
+    def _read_back(self, result, n):
         host = self._readback[self._readback_at % len(self._readback)][:result.numel()]
         self._readback_at += 1
         host.copy_(result, non_blocking=True)        # the step's only device->host read
         done = torch.cuda.Event()
         done.record()
         return host, done, n
+
+    def _prefill_body(self, seqs, temps):
+        input_ids = self.prepare_prefill(seqs)
+        tokens = self.next_tokens(self.run_model(input_ids, True), temps)
+        slots = torch.tensor([s.slot for s in seqs], dtype=torch.int64).pin_memory().to(self.device,
+                                                                                         non_blocking=True)
+        self.state.last_token.index_copy_(0, slots, tokens)
+        return torch.cat([tokens, self.error_word.to(torch.int64)])
+
+    def _launch_prefill_lane(self, seqs):
+        """A prefill wave on the next of the two side streams.  The wave before it may still be running on the
+        other one: the waves touch different sequences (rows of the state tables, cache blocks), every tensor of
+        a wave is allocated on its stream, and a wave that reads cached blocks waits for the other stream first
+        (the blocks may have been written there)."""
+        lane = self._prefill_at % len(self.prefill_lanes)
+        self._prefill_at += 1
+        stream, comm = self.prefill_lanes[lane]
+        main = torch.cuda.current_stream()
+        stream.wait_stream(main)
+        if any(s.num_cached_tokens for s in seqs):
+            for other, _ in self.prefill_lanes:
+                if other is not stream:
+                    stream.wait_stream(other)
+        if comm is not None:
+            comm.set_max_blocks(self.prefill_comm_blocks)
+            self.model.comm = comm
+        try:
+            with torch.cuda.stream(stream):
+                result = self._prefill_body(seqs, None)
+                reset_context()
+                if self._readback is None:
+                    self._readback = [torch.empty(max(self.max_num_seqs, self.max_num_batched_tokens) + 1,
+                                                  dtype=torch.int64).pin_memory() for _ in range(4)]
+                return self._read_back(result, len(seqs))
+        finally:
+            if comm is not None:
+                comm.set_max_blocks(0)
+                self.model.comm = self.comm
 
     def finish(self, handle):
         """Waits for a launched step; raises if a kernel wait of the step ran out of time."""
@@ -359,6 +421,10 @@ class ModelRunner:
             self.model.comm = None
             if self.world_size > 1:
                 dist.barrier()           # no rank unmaps while a peer may still be inside a kernel
+            for _, comm in self.prefill_lanes:
+                if comm is not None and comm is not self.comm:
+                    comm.close()
+            self.prefill_lanes = []
             self.comm.close()
             self.comm = None
         torch.cuda.synchronize()

@@ -52,6 +52,11 @@ class _CommBase:
         """After a timed-out wait, on every rank and with every rank idle: zero the flags and generations."""
         _cabi.check(_cabi.lib().mv_comm_reset(self._comm))
 
+    def set_max_blocks(self, max_blocks):
+        """Caps the grid of the following calls (0 = no cap): a block of the kernel holds a whole SM, and a
+        caller that overlaps a bandwidth-bound call with another stream's GEMMs leaves them the rest."""
+        _cabi.check(_cabi.lib().mv_comm_set_max_blocks(self._comm, int(max_blocks)))
+
 
 class TPCommunicator(_CommBase):
     """One per rank.  `max_rows` x `hidden` bounds a single call (the largest prefill wave)."""

@@ -215,3 +215,14 @@ def test_engine_configuration_3_streams_against_oracle_attention():
     print(f"\nconfiguration 3: {identical}/{len(prompts)} requests token-identical for 32 tokens; the others part at "
           f"verified near-ties")
     assert identical >= 57
+
+
+def test_two_prefill_waves_in_flight_keep_the_streams():
+    """prefill_streams=2: prefill waves alternate between two side streams and overlap on the GPU; the token
+    streams are those of the one-stream engine.  max_num_batched_tokens is small so that
+    the six prompts make several waves, and the second configuration also preempts and prefills again."""
+    for extra in (dict(max_num_batched_tokens=48), dict(max_num_batched_tokens=48, num_kv_blocks=9)):
+        one, _ = _run(False, max_tokens=24, config=dict(CONFIG, prefill_streams=1, **extra))
+        two, eng = _run(False, max_tokens=24, config=dict(CONFIG, prefill_streams=2, **extra))
+        assert eng.model_runner._prefill_at >= 3, "the prompts were meant to take several waves"
+        _assert_same_up_to_near_ties(two, one, "two prefill streams against one", config=dict(CONFIG, **extra))

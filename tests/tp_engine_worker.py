@@ -1,7 +1,8 @@
 """One rank of the multi-GPU engine test (launched by tests/test_allreduce_multigpu.py, one process per GPU).
 
 Runs the same requests through the engine at TP = world size (heads and MLP sharded, fused all-reduce + residual +
-RMSNorm over peer memory, residual stream sharded by rows; eager and CUDA-graph decode must agree) and through a
+RMSNorm over peer memory, residual stream sharded by rows; eager and CUDA-graph decode must agree, and so must
+two prefill waves in flight on two streams (prefill_streams=2) against one stream) and through a
 TP = 1 engine built on the same GPU, and compares the final hidden states that reach the LM head at every step in which both
 engines fed the same tokens (a random-init model's logits are nearly flat, so greedy streams may part at a
 near-tie; what must hold is that equal inputs give equal activations up to bf16 rounding).  Prints
@@ -25,8 +26,8 @@ CONFIG = dict(vocab_size=2048, hidden_size=512, num_layers=3, num_heads=8, num_k
               eos=-1, seed=0, dtype=torch.bfloat16)
 
 
-def run(world, rank, prompts, steps, eager=True):
-    eng = LLMEngine(dict(CONFIG, world_size=world, enforce_eager=eager), rank=rank if world > 1 else 0,
+def run(world, rank, prompts, steps, eager=True, **over):
+    eng = LLMEngine(dict(CONFIG, world_size=world, enforce_eager=eager, **over), rank=rank if world > 1 else 0,
                     world_size=world)
     model, seen = eng.model_runner.model, []
     inner = model.compute_logits
@@ -39,9 +40,9 @@ def run(world, rank, prompts, steps, eager=True):
         return inner(hidden, *a, **k)
     model.compute_logits = spy
     out = eng.generate(prompts, SamplingParams(temperature=0.0, max_tokens=steps, ignore_eos=True))["token_ids"]
-    note = eng.model_runner.comm_note
+    note, waves = eng.model_runner.comm_note, eng.model_runner._prefill_at
     eng.exit()
-    return out, seen, note
+    return out, seen, (note, waves) if over else note
 
 
 def main():
@@ -71,6 +72,12 @@ def main():
     dist.all_gather_object(every, tp_tokens)
     assert all(e == every[0] for e in every), "ranks generated different tokens"
     same = sum(a == b for a, b in zip(tp_tokens, one_tokens))
+    # Several prefill waves: with prefill_streams=2 two of them are in flight on two streams, each with its own communicator
+    # and a capped all-reduce grid; the tokens must be those of the one-stream engine (same kernels, same sums).
+    two, _, (_, waves) = run(world, rank, prompts, steps, eager=False, max_num_batched_tokens=64, prefill_streams=2)
+    one, _, (_, none) = run(world, rank, prompts, steps, eager=False, max_num_batched_tokens=64, prefill_streams=1)
+    assert waves >= 3 and none == 0, (waves, none)
+    assert two == one, "two prefill waves in flight changed the tokens"
     dist.barrier()
     dist.destroy_process_group()
     print("TP_ENGINE_OK", rank, compared, f"identical streams {same}/{len(prompts)}", flush=True)
