@@ -512,10 +512,8 @@ class EngineWorkload:
         self.rank, self.world, self.device = rank, world, device
         if os.environ.get("MV_CUSTOM_ALLREDUCE", "1") == "0":      # A/B switch: the NCCL all-reduce path
             cfg_over.setdefault("custom_allreduce", False)
-        if os.environ.get("MV_PREFILL_STREAMS"):                   # A/B switch: 1 = one prefill wave at a time
+        if os.environ.get("MV_PREFILL_STREAMS"):                   # A/B switch: 2 = two prefill waves in flight
             cfg_over.setdefault("prefill_streams", int(os.environ["MV_PREFILL_STREAMS"]))
-        if os.environ.get("MV_PREFILL_COMM_BLOCKS"):               # grid cap of the all-reduce beside another wave
-            cfg_over.setdefault("prefill_comm_blocks", int(os.environ["MV_PREFILL_COMM_BLOCKS"]))
         self.cfg = configs.qwen3_8b_config(world_size=world, **cfg_over)
         self.prompts, self.sp = configs.qwen3_8b_requests(n=requests, new_tokens=new_tokens)
         self.engine = LLMEngine(self.cfg, rank=rank, world_size=world)

@@ -625,12 +625,12 @@ static int launch_allreduce(Comm* c, void* residual, int64_t residual_slot_strid
   const int rows_per = (rows + c->world - 1) / c->world;
   int at_once = comm_rows_at_once(rows_per, c->world, vpt, threads);
   int blocks = comm_grid(rows_per, at_once, threads);
-  if (c->max_blocks > 0 && blocks > c->max_blocks) blocks = c->max_blocks;
   if (c->emulated) {            // all ranks share one GPU: one row at a time, and few enough blocks to be co-resident
     at_once = 1;
     blocks = comm_grid(rows_per, 1, threads);
     if (blocks * c->slots > kNumSMs) blocks = kNumSMs / c->slots;
   }
+  if (c->max_blocks > 0 && blocks > c->max_blocks) blocks = c->max_blocks;
   const dim3 grid(blocks, c->slots);
 #define MV_AR(W, R, V) \
   return launch_allreduce_as<T, W, R, V>(c, grid, threads, residual, residual_slot_stride, gamma, eps, rows, hidden, error_word, stream)

@@ -62,19 +62,22 @@ class ModelRunner:
         self.comm, self.comm_note = None, "single rank"
         if self.world_size > 1:
             self._attach_communicator()
-        # prefill_streams=2: two prefill waves in flight on two streams, each with a communicator of its own, so
-        # that one wave's all-reduces (NVLink-bound, a capped number of SMs) can run beside the other wave's GEMMs.
-        # Off by default: the all-reduce kernel keeps one row group in flight per block and needs most SMs to
-        # fill the link (16,384 rows on 2 GPUs: 220 us on 296 blocks, 486 us on 48), so the overlap gains
-        # nothing yet.  Greedy runs only: a sampled run advances one step counter in stream order.
+        # prefill_streams=2: two prefill waves in flight on two streams, so that one wave's all-reduces (bound by
+        # the link) run beside the other wave's GEMMs.  On the side streams the reduction is NCCL reduce-scatter +
+        # add + norm on the owned rows + all-gather, one process group per stream (layers/allreduce.py): NCCL
+        # fills the link from a few SMs, the fused peer-memory kernel needs most of them (16,384 rows on 2 GPUs:
+        # 220 us on 296 blocks, 486 us on 48) and stays the kernel of decode steps and of one-stream prefill.
+        # Greedy runs only: a sampled run advances one step counter in stream order.
         self.prefill_lanes, self._prefill_at = [], 0
         want = int(config.get("prefill_streams", 1))
         if want >= 2 and self.greedy and self.device.type == "cuda":
-            second = self._new_communicator() if self.comm is not None else None
-            if self.comm is None or second is not None:
-                self.prefill_lanes = [(torch.cuda.Stream(device=self.device), self.comm),
-                                      (torch.cuda.Stream(device=self.device), second)]
-        self.prefill_comm_blocks = int(config.get("prefill_comm_blocks", 48))
+            for _ in range(2):
+                comm = None
+                if self.comm is not None:
+                    from ..layers.allreduce import NcclLaneCommunicator
+                    comm = NcclLaneCommunicator(self.rank, self.world_size, self.max_num_batched_tokens,
+                                                self.model_cfg.hidden_size, self.dtype, self.device, dist.new_group())
+                self.prefill_lanes.append((torch.cuda.Stream(device=self.device), comm))
         self.error_word = _error_word(self.device)
         self.max_blocks_per_seq = math.ceil(self.max_model_len / self.block_size)
         # one spare slot: padded rows of a captured batch point at it
@@ -334,7 +337,6 @@ class ModelRunner:
                 if other is not stream:
                     stream.wait_stream(other)
         if comm is not None:
-            comm.set_max_blocks(self.prefill_comm_blocks)
             self.model.comm = comm
         try:
             with torch.cuda.stream(stream):
@@ -346,7 +348,6 @@ class ModelRunner:
                 return self._read_back(result, len(seqs))
         finally:
             if comm is not None:
-                comm.set_max_blocks(0)
                 self.model.comm = self.comm
 
     def finish(self, handle):
@@ -422,7 +423,7 @@ class ModelRunner:
             if self.world_size > 1:
                 dist.barrier()           # no rank unmaps while a peer may still be inside a kernel
             for _, comm in self.prefill_lanes:
-                if comm is not None and comm is not self.comm:
+                if comm is not None:
                     comm.close()
             self.prefill_lanes = []
             self.comm.close()

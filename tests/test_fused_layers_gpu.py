@@ -105,6 +105,19 @@ def test_emulated_allreduce_other_widths():
             comm.close()
 
 
+def test_a_capped_grid_gives_the_same_rows():
+    """mv_comm_set_max_blocks: rows are strided over however many blocks there are; the barriers do not depend on
+    the grid."""
+    comm = EmulatedCommunicator(4, 64, 4096, torch.bfloat16, DEV)
+    try:
+        for cap in (1, 3, 0):
+            comm.set_max_blocks(cap)
+            _emulated_case(comm, 64, 4096, torch.bfloat16, seed=7 + cap)
+            _emulated_case(comm, 13, 4096, torch.bfloat16, seed=70 + cap)
+    finally:
+        comm.close()
+
+
 def test_withheld_signal_times_out_and_reports():
     """A rank that never signals: the others' waits run out (200 ms limit), the error word is set, the launch
     ends by itself and later launches return at once; after a reset the communicator works again."""
