@@ -152,7 +152,9 @@ int mv_paged_decode_static(void* out, const void* q,
  * 128); q/k/v take a token stride in elements (heads dense within a token),
  * out is contiguous.  fp32 accumulation on the tcgen05 tensor cores.
  * No host synchronisation: the grid is an upper bound computed from
- * total_tokens and num_seqs.
+ * total_tokens and num_seqs, or (up to 320 sequences) one block per SM that
+ * takes query tiles from a work counter inside the library; a launch uses
+ * the next of 1,024 counters and leaves it zeroed, nothing is allocated.
  * error_word points to one zero-initialised int in device memory that the
  * caller keeps: a kernel wait that runs out of time stores a non-zero code
  * there (and later launches return at once until the caller clears it).
