@@ -73,6 +73,11 @@ enum { BAR_Q = 0, BAR_KFULL = 1, BAR_KEMPTY = 3, BAR_VFULL = 5, BAR_VEMPTY = 7, 
 #ifdef MV_PF_TRACE
 // Timeline probe (debug builds only, -DMV_PF_TRACE): one thread of each role of ONE CTA writes clock64()
 // stamps per KV step, so that the phases of the pipeline can be read off without a profiler.
+// Buffer (long long, 2048 entries, set with mv_debug_prefill_trace): entry ((role * 32 + i) * 8 + k) is stamp k
+// of role `role` at index i.  One CTA per tile: i = KV step.  Persistent kernel: i = the CTA's unit number,
+// roles 0 producer, 1 MMA warp, 2 / 3 first softmax warp of head A / B (entry k = 7 of role 0 holds the unit's
+// number of KV steps); PF_STEP adds, from entry 1024 on, per-step stamps of the CTA's fourth unit
+// ((role * 8 + step) * 8 + k; roles 0 MMA warp, 1 / 2 softmax A / B).
 __device__ long long* g_pf_trace = nullptr;
 __device__ int g_pf_trace_cta = -1;
 // pf_tr is read once per thread at kernel start: a stamp is then one predicated store, cheap enough not to
