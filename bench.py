@@ -553,8 +553,11 @@ class EngineWorkload:
         prefill_waves = s["steps"] - decode_steps
         tail = (2 if self.world > 1 else 1) if self.cfg.get("greedy", False) else 0
         # per layer: fused q/k norm + RoPE + store, attention (one launch in decode and in prefill), two fused
-        # (all-reduce +) add + norm kernels, SwiGLU activation; per step: the first norm and the metadata kernel(s)
-        return decode_steps * (layers * 5 + 2 + tail) + prefill_waves * (layers * 5 + 3 + tail)
+        # (all-reduce +) add + norm kernels, SwiGLU activation; per step: the first norm and the metadata kernel(s).
+        # A prefill wave on a side stream takes the copy-engine form of the all-reduce: two barrier kernels and
+        # one reduction kernel per call instead of the one fused kernel.
+        staged = 2 * 2 if self.engine.model_runner.prefill_lanes and self.world > 1 else 0
+        return decode_steps * (layers * 5 + 2 + tail) + prefill_waves * (layers * (5 + staged) + 3 + tail)
 
     def decode_probe(self, iters=36):
         """Times paged_attention_decode with CUDA events on the engine's own KV pool at the shape of the

@@ -378,6 +378,17 @@ int mv_allreduce_residual_rmsnorm(void* comm, void* residual_shard,
                                   const void* gamma, float eps, int rows,
                                   int hidden, int* error_word, int dtype,
                                   void* stream);
+/* The same step (arguments, result, row ownership, error codes, bounded waits) with the two bulk transfers done
+ * by the copy engines: barrier, cudaMemcpyAsync of the peers' partial rows of this rank's shard into staging
+ * inside the communicator, one local kernel (the same sums and roundings), cudaMemcpyAsync of the normalised
+ * rows to every peer, barrier.  For messages that are bound by the link (a prefill wave): the SMs stay free
+ * while the bytes move, so another stream's work runs beside it.  Calls of both forms may follow each other on
+ * one communicator. */
+int mv_allreduce_residual_rmsnorm_staged(void* comm, void* residual_shard,
+                                  int64_t residual_slot_stride,
+                                  const void* gamma, float eps, int rows,
+                                  int hidden, int* error_word, int dtype,
+                                  void* stream);
 
 /*
  * Single-rank form of the same step: for every row,

@@ -62,6 +62,8 @@ SIGNATURES = {
     "mv_comm_output": (_c_ptr, [_c_ptr, _c_int]),
     "mv_allreduce_residual_rmsnorm": (_c_int, [_c_ptr, _c_ptr, _c_i64, _c_ptr, _c_f32, _c_int, _c_int, _c_ptr,
                                                _c_int, _c_ptr]),
+    "mv_allreduce_residual_rmsnorm_staged": (_c_int, [_c_ptr, _c_ptr, _c_i64, _c_ptr, _c_f32, _c_int, _c_int, _c_ptr,
+                                               _c_int, _c_ptr]),
     "mv_add_rmsnorm": (_c_int, [_c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_i64, _c_i64, _c_ptr, _c_f32, _c_i64, _c_int,
                                 _c_int, _c_ptr]),
     "mv_silu_mul": (_c_int, [_c_ptr, _c_ptr, _c_i64, _c_i64, _c_int, _c_int, _c_ptr]),

@@ -78,6 +78,8 @@ struct Comm {
   unsigned long long timeout_ns = 0;
   int device = 0;
   int max_blocks = 0;                 // 0 = as many as the rows want; else a cap (mv_comm_set_max_blocks)
+  char* stage = nullptr;              // staged form: peers' partial rows land here ((world-1) slots per rank slot)
+  size_t stage_slot_bytes = 0;
 };
 
 // Control region layout (byte offsets inside a rank's region).
@@ -316,6 +318,103 @@ allreduce_residual_rmsnorm_kernel(CommSlot* __restrict__ table, void* __restrict
 }
 
 // ---------------------------------------------------------------------------------------------
+// The same step with the two bulk transfers done by the copy engines ("staged" form)
+// ---------------------------------------------------------------------------------------------
+// For messages that are bound by the link (a prefill wave: 128 MiB): ready barrier -> cudaMemcpyAsync of the
+// peers' partial rows of this rank's shard into local staging -> one local kernel (sum in rank order, residual,
+// norm; the same arithmetic and roundings as the fused kernel) -> cudaMemcpyAsync of the normalised rows into
+// every peer's gather buffer -> done barrier.  The SMs are free while the bytes move, so another stream's
+// GEMMs run beside it (the fused kernel keeps one group of rows in flight per block and needs most SMs to
+// fill the link).  The barriers are the fused kernel's, in two one-warp kernels: phase 0 = "my partial sums
+// are complete" / wait for the peers'; phase 1 = "my rows have landed at every peer" / wait, then the
+// generation advances.  Same flags, same generation counter, same bounded waits and error codes, so calls of
+// both forms can follow each other on one communicator.
+__global__ void __launch_bounds__(32)
+comm_barrier_kernel(CommSlot* __restrict__ table, int phase, unsigned long long timeout_ns, int* __restrict__ error_word) {
+  CommSlot& slot = table[0];
+  const int rank = slot.rank, world = slot.world, tid = threadIdx.x;
+  CommCtrl* mine = slot.ctrl[rank];
+  if (*reinterpret_cast<volatile int*>(error_word) != 0) return;     // an earlier wait ran out: do nothing
+  const uint32_t gen = *reinterpret_cast<volatile uint32_t*>(&mine->gen[0]) + 1;
+  bool ok = true;
+  if (phase == 1) __threadfence_system();
+  if (tid < world && tid != rank) {
+    if (phase == 0) {
+      if (!slot.skip_signal) st_release_sys(&slot.ctrl[tid]->ready[rank][0], gen);
+      ok = wait_flag(&mine->ready[tid][0], gen, timeout_ns);
+      if (!ok) atomicCAS(error_word, 0, 0x100 | tid);
+    } else {
+      st_release_sys(&slot.ctrl[tid]->done[rank][0], gen);
+      ok = wait_flag(&mine->done[tid][0], gen, timeout_ns);
+      if (!ok) atomicCAS(error_word, 0, 0x200 | tid);
+    }
+  }
+  ok = __all_sync(0xffffffffu, ok);
+  if (phase == 1 && ok && tid == 0) mine->gen[0] = gen;              // ready for the next launch
+}
+
+struct StagedRows {
+  const void* src[kMaxRanks];   // src[p] = rank p's partial sums of the owned rows, first owned row first
+};
+
+// One block per owned row at a time: sum over the ranks in order, round, add the residual, round, norm.
+template <typename T, int VPT>
+__global__ void __launch_bounds__(1024, 1)
+reduce_staged_kernel(const StagedRows in, int world, void* __restrict__ out_, void* __restrict__ residual_,
+                     const void* __restrict__ gamma_, float eps, int n_rows, int hidden,
+                     const int* __restrict__ error_word) {
+  __shared__ float red[33];
+  if (*reinterpret_cast<const volatile int*>(error_word) != 0) return;   // the ready barrier gave up
+  const int tid = threadIdx.x, nvec = hidden >> 3;
+  const uint4* gamma = reinterpret_cast<const uint4*>(gamma_);
+  uint4* residual = reinterpret_cast<uint4*>(residual_);
+  uint4* out = reinterpret_cast<uint4*>(out_);
+  const float inv_hidden = 1.0f / static_cast<float>(hidden);
+  for (int row = blockIdx.x; row < n_rows; row += gridDim.x) {
+    uint4 keep[VPT];
+    float ss = 0.f;
+#pragma unroll
+    for (int v = 0; v < VPT; ++v) {
+      const int c = tid + v * blockDim.x;
+      if (c < nvec) {
+        const size_t off = static_cast<size_t>(row) * nvec + c;
+        float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f}, f[8];
+        for (int p = 0; p < world; ++p) {
+          Vec8<T>::unpack(ld_global16(reinterpret_cast<const uint4*>(in.src[p]) + off), f);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) acc[i] += f[i];
+        }
+        const uint4 o = Vec8<T>::pack(acc);
+        Vec8<T>::unpack(o, acc);
+        Vec8<T>::unpack(residual[off], f);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) acc[i] += f[i];
+        const uint4 rn = Vec8<T>::pack(acc);
+        residual[off] = rn;
+        keep[v] = rn;
+        Vec8<T>::unpack(rn, f);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) ss += f[i] * f[i];
+      }
+    }
+    ss = block_sum(ss, red);
+    const float rstd = rsqrtf(ss * inv_hidden + eps);
+#pragma unroll
+    for (int v = 0; v < VPT; ++v) {
+      const int c = tid + v * blockDim.x;
+      if (c < nvec) {
+        float gf[8], h[8];
+        Vec8<T>::unpack(gamma[c], gf);
+        Vec8<T>::unpack(keep[v], h);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) h[i] = h[i] * rstd * gf[i];
+        out[static_cast<size_t>(row) * nvec + c] = Vec8<T>::pack(h);
+      }
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
 // local form: h = RMSNorm(x (+ residual)) for every row; the sum is stored for rows [res_lo, res_hi)
 // ---------------------------------------------------------------------------------------------
 template <typename T, int VPT>
@@ -429,6 +528,14 @@ static int cuda_fail(const char* what, cudaError_t e) {
   return fail(MV_ERR_CUDA, "%s: %s", what, cudaGetErrorString(e));
 }
 
+// Staging of the staged form: per rank slot, one buffer per peer for that peer's partial sums of the slot's rows
+// (a shard is ceil(rows/world) rows, so a slot takes data_bytes/world plus one row of slack).
+static int alloc_stage(Comm* c) {
+  c->stage_slot_bytes = round256(static_cast<size_t>(c->data_bytes) / c->world + 16384 * 2);
+  const cudaError_t e = cudaMalloc(reinterpret_cast<void**>(&c->stage), c->stage_slot_bytes * (c->world - 1) * c->slots);
+  return e == cudaSuccess ? MV_OK : cuda_fail("comm: staging buffers", e);
+}
+
 static int write_table(Comm* c) {
   CommSlot host[kMaxRanks] = {};
   for (int s = 0; s < c->slots; ++s) {
@@ -498,6 +605,8 @@ extern "C" int mv_comm_connect(void* comm, const void* all_handles) {
   }
   const int rc = write_table(c);
   if (rc) return rc;
+  const int rs = alloc_stage(c);
+  if (rs) return rs;
   c->connected = true;
   return MV_OK;
 }
@@ -526,7 +635,8 @@ extern "C" int mv_comm_create_emulated(int world, int64_t data_bytes, int timeou
   }
   for (int p = 0; p < world; ++p) c->region[p] = all + c->region_bytes * p;
   c->table_dev = reinterpret_cast<CommSlot*>(c->region[0] + kOffTable);
-  const int rc = write_table(c);
+  int rc = write_table(c);
+  if (!rc) rc = alloc_stage(c);
   if (rc) {
     cudaFree(all);
     delete c;
@@ -541,6 +651,7 @@ extern "C" int mv_comm_destroy(void* comm) {
   Comm* c = static_cast<Comm*>(comm);
   if (!c) return MV_OK;
   cudaDeviceSynchronize();
+  if (c->stage) cudaFree(c->stage);
   if (c->emulated) {
     cudaFree(c->region[0]);
   } else {
@@ -681,6 +792,103 @@ extern "C" int mv_allreduce_residual_rmsnorm(void* comm, void* residual_shard, i
   if (dtype == MV_BF16)
     return launch_allreduce<__nv_bfloat16>(c, residual_shard, residual_slot_stride, gamma, eps, rows, hidden, error_word, s);
   return fail(MV_ERR_DTYPE, "allreduce_residual_rmsnorm: dtype %d", dtype);
+}
+
+template <typename T>
+static int launch_staged(Comm* c, void* residual_shard, int64_t residual_slot_stride, const void* gamma, float eps,
+                         int rows, int hidden, int* error_word, cudaStream_t st) {
+  int vpt = 1;
+  const int threads = threads_for(hidden, &vpt);
+  const int rows_per = (rows + c->world - 1) / c->world;
+  const size_t row_bytes = static_cast<size_t>(hidden) * 2;
+  if (static_cast<size_t>(rows_per) * row_bytes > c->stage_slot_bytes)
+    return fail(MV_ERR_LIMIT, "allreduce_residual_rmsnorm_staged: a shard of %d rows exceeds the staging buffers", rows_per);
+  const size_t out_off = kCtrlBytes + round256(static_cast<size_t>(c->data_bytes));
+  cudaError_t e = cudaSuccess;
+  if (!c->emulated) {
+    comm_barrier_kernel<<<1, 32, 0, st>>>(c->table_dev, 0, c->timeout_ns, error_word);
+    if (int rc = check_launch("comm_barrier_kernel")) return rc;
+  }
+  // Every rank slot in turn (one in a real communicator): pull, reduce, push.  In emulation all pulls come
+  // first, then all reductions, then all pushes: stream order stands in for the barriers.
+  for (int phase = 0; phase < 3; ++phase) {
+    for (int sl = 0; sl < c->slots; ++sl) {
+      const int r = c->emulated ? sl : c->rank;
+      const int lo = rows_per * r < rows ? rows_per * r : rows;
+      const int hi = lo + rows_per < rows ? lo + rows_per : rows;
+      const int n = hi - lo;
+      if (n <= 0) continue;
+      char* stage = c->stage + c->stage_slot_bytes * (c->world - 1) * sl;
+      char* mine = c->region[r];
+      if (phase == 0) {
+        for (int k = 1; k < c->world && e == cudaSuccess; ++k) {      // start at the next rank: spreads the load
+          const int p = (r + k) % c->world;
+          e = cudaMemcpyAsync(stage + c->stage_slot_bytes * (k - 1), c->region[p] + kCtrlBytes + lo * row_bytes,
+                              n * row_bytes, cudaMemcpyDefault, st);
+        }
+      } else if (phase == 1) {
+        StagedRows in;
+        for (int p = 0; p < kMaxRanks; ++p) in.src[p] = nullptr;
+        in.src[r] = mine + kCtrlBytes + lo * row_bytes;
+        for (int k = 1; k < c->world; ++k) in.src[(r + k) % c->world] = stage + c->stage_slot_bytes * (k - 1);
+        T* residual = static_cast<T*>(residual_shard) + static_cast<int64_t>(sl) * residual_slot_stride;
+        const int grid = n < 4 * kNumSMs ? n : 4 * kNumSMs;
+        void* out = mine + out_off + lo * row_bytes;
+        if (vpt == 1)
+          reduce_staged_kernel<T, 1><<<grid, threads, 0, st>>>(in, c->world, out, residual, gamma, eps, n, hidden, error_word);
+        else
+          reduce_staged_kernel<T, 2><<<grid, threads, 0, st>>>(in, c->world, out, residual, gamma, eps, n, hidden, error_word);
+        if (int rc = check_launch("reduce_staged_kernel")) return rc;
+      } else {
+        for (int k = 1; k < c->world && e == cudaSuccess; ++k) {
+          const int p = (r + k) % c->world;
+          e = cudaMemcpyAsync(c->region[p] + out_off + lo * row_bytes, mine + out_off + lo * row_bytes, n * row_bytes,
+                              cudaMemcpyDefault, st);
+        }
+      }
+    }
+    if (e != cudaSuccess) return cuda_fail("allreduce_residual_rmsnorm_staged: cudaMemcpyAsync", e);
+  }
+  if (!c->emulated) {
+    comm_barrier_kernel<<<1, 32, 0, st>>>(c->table_dev, 1, c->timeout_ns, error_word);
+    if (int rc = check_launch("comm_barrier_kernel")) return rc;
+  }
+  return MV_OK;
+}
+
+// Same arguments, result and error codes as mv_allreduce_residual_rmsnorm; the bulk transfers run on the copy
+// engines (see the staged form above).  Not for CUDA graphs that are replayed while the peers' buffers move:
+// the copies are captured with the addresses they were issued with, which is what a replay wants here too.
+extern "C" int mv_allreduce_residual_rmsnorm_staged(void* comm, void* residual_shard, int64_t residual_slot_stride,
+                                                    const void* gamma, float eps, int rows, int hidden, int* error_word,
+                                                    int dtype, void* stream) {
+  Comm* c = static_cast<Comm*>(comm);
+  if (!c || !gamma || !error_word) return fail(MV_ERR_NULL, "allreduce_residual_rmsnorm_staged: null argument");
+  if (!c->connected) return fail(MV_ERR_SHAPE, "allreduce_residual_rmsnorm_staged: communicator is not connected");
+  if (!residual_shard) {      // allowed only for a rank that owns no row of this call
+    const int per = rows > 0 ? (rows + c->world - 1) / c->world : 0;
+    if (c->emulated || static_cast<int64_t>(c->rank) * per < rows)
+      return fail(MV_ERR_NULL, "allreduce_residual_rmsnorm_staged: residual_shard is null but this rank owns rows");
+  }
+  if (rows < 0 || hidden <= 0 || hidden % 8 != 0)
+    return fail(MV_ERR_SHAPE, "allreduce_residual_rmsnorm_staged: hidden (%d) must be a positive multiple of 8, rows >= 0", hidden);
+  if (hidden > 16384) return fail(MV_ERR_LIMIT, "allreduce_residual_rmsnorm_staged: hidden %d exceeds 16384", hidden);
+  if (static_cast<int64_t>(rows) * hidden * 2 > c->data_bytes)
+    return fail(MV_ERR_LIMIT, "allreduce_residual_rmsnorm_staged: %d rows x %d exceed the communicator's %lld-byte buffers",
+                rows, hidden, static_cast<long long>(c->data_bytes));
+  if (!aligned16(residual_shard) || !aligned16(gamma) || (residual_slot_stride * 2) % 16 != 0)
+    return fail(MV_ERR_ALIGN, "allreduce_residual_rmsnorm_staged: residual and gamma must be 16-byte aligned");
+  if (c->emulated) {
+    const int rows_per = (rows + c->world - 1) / c->world;
+    if (c->slots > 1 && residual_slot_stride < static_cast<int64_t>(rows_per) * hidden)
+      return fail(MV_ERR_SHAPE, "allreduce_residual_rmsnorm_staged: residual_slot_stride smaller than one rank's shard");
+  }
+  if (rows == 0) return MV_OK;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (dtype == MV_F16) return launch_staged<__half>(c, residual_shard, residual_slot_stride, gamma, eps, rows, hidden, error_word, s);
+  if (dtype == MV_BF16)
+    return launch_staged<__nv_bfloat16>(c, residual_shard, residual_slot_stride, gamma, eps, rows, hidden, error_word, s);
+  return fail(MV_ERR_DTYPE, "allreduce_residual_rmsnorm_staged: dtype %d", dtype);
 }
 
 extern "C" int mv_add_rmsnorm(void* out, const void* x, const void* residual_in, void* residual_out, int64_t res_lo,

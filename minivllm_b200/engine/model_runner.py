@@ -62,22 +62,27 @@ class ModelRunner:
         self.comm, self.comm_note = None, "single rank"
         if self.world_size > 1:
             self._attach_communicator()
-        # prefill_streams=2: two prefill waves in flight on two streams, so that one wave's all-reduces (bound by
-        # the link) run beside the other wave's GEMMs.  On the side streams the reduction is NCCL reduce-scatter +
-        # add + norm on the owned rows + all-gather, one process group per stream (layers/allreduce.py): NCCL
-        # fills the link from a few SMs, the fused peer-memory kernel needs most of them (16,384 rows on 2 GPUs:
-        # 220 us on 296 blocks, 486 us on 48) and stays the kernel of decode steps and of one-stream prefill.
-        # Greedy runs only: a sampled run advances one step counter in stream order.
+        # prefill_streams=2 (the default under tensor parallelism): two prefill waves in flight on two streams, so
+        # that one wave's all-reduces (bound by the link) run beside the other wave's GEMMs.  Each stream has a
+        # communicator of its own whose calls take the copy-engine form (layers/allreduce.py, staged=True): the
+        # fused kernel needs most SMs to fill the link, the copy engines need none; the sums and roundings are
+        # the same, so the tokens are those of the one-stream engine.  Greedy runs only: a sampled run advances
+        # one step counter in stream order.
         self.prefill_lanes, self._prefill_at = [], 0
-        want = int(config.get("prefill_streams", 1))
+        want = int(config.get("prefill_streams", 2 if self.comm is not None else 1))
         if want >= 2 and self.greedy and self.device.type == "cuda":
+            lanes = []
             for _ in range(2):
-                comm = None
-                if self.comm is not None:
-                    from ..layers.allreduce import NcclLaneCommunicator
-                    comm = NcclLaneCommunicator(self.rank, self.world_size, self.max_num_batched_tokens,
-                                                self.model_cfg.hidden_size, self.dtype, self.device, dist.new_group())
-                self.prefill_lanes.append((torch.cuda.Stream(device=self.device), comm))
+                comm = self._new_communicator(staged=True) if self.comm is not None else None
+                if self.comm is not None and comm is None:
+                    break
+                lanes.append((torch.cuda.Stream(device=self.device), comm))
+            if len(lanes) == 2:
+                self.prefill_lanes = lanes
+            else:
+                for _, comm in lanes:
+                    if comm is not None:
+                        comm.close()
         self.error_word = _error_word(self.device)
         self.max_blocks_per_seq = math.ceil(self.max_model_len / self.block_size)
         # one spare slot: padded rows of a captured batch point at it
@@ -192,13 +197,14 @@ class ModelRunner:
             if self.rank == 0:
                 print("minivllm_b200: " + self.comm_note, flush=True)
 
-    def _new_communicator(self):
+    def _new_communicator(self, staged=False):
         """A peer-memory communicator for this rank, or None on EVERY rank if any rank could not set it up."""
         from ..layers.allreduce import TPCommunicator
         err, comm = "", None
         try:
             comm = TPCommunicator(self.rank, self.world_size, self.max_num_batched_tokens, self.model_cfg.hidden_size,
-                                  self.dtype, self.device, timeout_ms=self.config.get("comm_timeout_ms", 5000))
+                                  self.dtype, self.device, timeout_ms=self.config.get("comm_timeout_ms", 5000),
+                                  staged=staged)
         except Exception as e:  # noqa: BLE001 - reported, and agreed on by all ranks below
             err = f"{type(e).__name__}: {e}"
         ok = torch.tensor([0 if err else 1], device=self.device, dtype=torch.int32)

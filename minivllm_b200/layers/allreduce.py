@@ -61,8 +61,9 @@ class _CommBase:
 class TPCommunicator(_CommBase):
     """One per rank.  `max_rows` x `hidden` bounds a single call (the largest prefill wave)."""
 
-    def __init__(self, rank, world, max_rows, hidden, dtype, device, group=None, timeout_ms=5000):
+    def __init__(self, rank, world, max_rows, hidden, dtype, device, group=None, timeout_ms=5000, staged=False):
         L = _cabi.lib()
+        self.staged = staged     # True: bulk transfers on the copy engines (mv_allreduce_residual_rmsnorm_staged)
         self.rank, self.world, self.max_rows, self.hidden, self.dtype = rank, world, max_rows, hidden, dtype
         self.device = torch.device(device)
         self.data_bytes = max_rows * hidden * 2
@@ -92,9 +93,10 @@ class TPCommunicator(_CommBase):
         """Reduces the first `rows` rows of every rank's input buffer.  residual_shard (owned rows, hidden) is
         updated in place; returns the (rows, hidden) gather buffer holding the normalised rows of all ranks
         (valid until the next call)."""
-        _cabi.check(_cabi.lib().mv_allreduce_residual_rmsnorm(
-            self._comm, residual_shard.data_ptr(), 0, gamma.data_ptr(), float(eps), rows, self.hidden,
-            self.error_word.data_ptr(), _cabi.dtype_code(self.dtype), _cabi.stream_ptr()))
+        L = _cabi.lib()
+        fn = L.mv_allreduce_residual_rmsnorm_staged if self.staged else L.mv_allreduce_residual_rmsnorm
+        _cabi.check(fn(self._comm, residual_shard.data_ptr(), 0, gamma.data_ptr(), float(eps), rows, self.hidden,
+                       self.error_word.data_ptr(), _cabi.dtype_code(self.dtype), _cabi.stream_ptr()))
         return self._out[:rows]
 
 
@@ -115,51 +117,14 @@ class EmulatedCommunicator(_CommBase):
         self.outputs = [self._wrap(L.mv_comm_output(comm, r)) for r in range(world)]
         self.error_word = torch.zeros(1, dtype=torch.int32, device=self.device)
 
-    def allreduce_residual_rmsnorm(self, rows, residual_shards, gamma, eps):
-        """residual_shards (world, rows_per_rank, hidden) contiguous: rank r's shard is residual_shards[r]."""
+    def allreduce_residual_rmsnorm(self, rows, residual_shards, gamma, eps, staged=False):
+        """residual_shards (world, rows_per_rank, hidden) contiguous: rank r's shard is residual_shards[r].
+        staged=True: the copy-engine form (the copies and the local kernel of every rank; the barrier kernels
+        only exist between real ranks)."""
         assert residual_shards.is_contiguous() and residual_shards.shape[0] == self.world
-        _cabi.check(_cabi.lib().mv_allreduce_residual_rmsnorm(
-            self._comm, residual_shards.data_ptr(), residual_shards.stride(0), gamma.data_ptr(), float(eps), rows,
-            self.hidden, self.error_word.data_ptr(), _cabi.dtype_code(self.dtype), _cabi.stream_ptr()))
+        L = _cabi.lib()
+        fn = L.mv_allreduce_residual_rmsnorm_staged if staged else L.mv_allreduce_residual_rmsnorm
+        _cabi.check(fn(self._comm, residual_shards.data_ptr(), residual_shards.stride(0), gamma.data_ptr(), float(eps),
+                       rows, self.hidden, self.error_word.data_ptr(), _cabi.dtype_code(self.dtype),
+                       _cabi.stream_ptr()))
         return [o[:rows] for o in self.outputs]
-
-
-class NcclLaneCommunicator:
-    """The same call as TPCommunicator.allreduce_residual_rmsnorm, made of NCCL reduce-scatter + this library's
-    add + RMSNorm kernel on the owned rows + NCCL all-gather, on a process group of its own.
-
-    For a prefill wave that runs beside another wave on a second stream (engine option `prefill_streams=2`): the
-    128 MiB messages of a wave are bound by the link, NCCL's kernels fill it from a few SMs, and the other wave's
-    GEMMs keep the rest -- the fused peer-memory kernel needs most SMs to do the same (one group of rows in
-    flight per block).  One group per lane: collectives of one group run in issue order, and a wave's first
-    reduction must not queue behind the other wave's last one.  The sums are NCCL's (bf16 partial sums as the
-    reference has them, src/myvllm/layers/linear.py:216-221), not the fused kernel's fp32 sums in rank order."""
-
-    def __init__(self, rank, world, max_rows, hidden, dtype, device, group):
-        self.rank, self.world, self.max_rows, self.hidden, self.dtype = rank, world, max_rows, hidden, dtype
-        self.device, self.group = torch.device(device), group
-        self.per_max = (max_rows + world - 1) // world
-        full = self.per_max * world
-        self._in = torch.zeros(full, hidden, dtype=dtype, device=self.device)
-        self._out = torch.zeros(full, hidden, dtype=dtype, device=self.device)
-        self._sum = torch.empty(self.per_max, hidden, dtype=dtype, device=self.device)
-        self._norm = torch.zeros(self.per_max, hidden, dtype=dtype, device=self.device)
-
-    def input_rows(self, rows):
-        return self._in[:rows]
-
-    def allreduce_residual_rmsnorm(self, rows, residual_shard, gamma, eps):
-        from .layernorm import add_rms_norm
-        per = (rows + self.world - 1) // self.world          # shard_rows(): rank r owns rows [r*per, (r+1)*per)
-        lo, hi = shard_rows(rows, self.rank, self.world)
-        # rows [rows, world*per) of the input are stale: they land in rows nobody reads
-        dist.reduce_scatter_tensor(self._sum[:per], self._in[:per * self.world], group=self.group)
-        if hi > lo:
-            add_rms_norm(self._sum[:hi - lo], residual_shard, gamma, eps, residual_out=residual_shard,
-                         out=self._norm[:hi - lo])
-        dist.all_gather_into_tensor(self._out[:per * self.world], self._norm[:per], group=self.group)
-        return self._out[:rows]
-
-    def close(self):
-        self._in = self._out = self._sum = self._norm = None
-

@@ -57,7 +57,7 @@ def test_silu_and_mul_matches_oracle(dtype):
     assert _ulp_close(silu_and_mul(view), oracle.silu_and_mul(view.cpu()), dtype)
 
 
-def _emulated_case(comm, rows, hidden, dtype, seed):
+def _emulated_case(comm, rows, hidden, dtype, seed, staged=False):
     world = comm.world
     g = torch.Generator().manual_seed(seed)
     partials = [torch.randn(rows, hidden, generator=g).to(dtype) for _ in range(world)]
@@ -72,7 +72,7 @@ def _emulated_case(comm, rows, hidden, dtype, seed):
     for r in range(world):
         comm.inputs[r][:rows].copy_(partials[r])
         comm.outputs[r][:rows].fill_(float("nan"))
-    outs = comm.allreduce_residual_rmsnorm(rows, shards, gamma.to(DEV), EPS)
+    outs = comm.allreduce_residual_rmsnorm(rows, shards, gamma.to(DEV), EPS, staged=staged)
     torch.cuda.synchronize()
     assert int(comm.error_word.item()) == 0
     want_h, want_r = oracle.allreduce_residual_rmsnorm(partials, residual, gamma, EPS)
@@ -103,6 +103,24 @@ def test_emulated_allreduce_other_widths():
             _emulated_case(comm, rows, hidden, torch.bfloat16, seed=hidden)
         finally:
             comm.close()
+
+
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_emulated_staged_form_matches_the_oracle(world):
+    """The copy-engine form: every rank's pulls, local reduction and pushes (the barrier kernels between real
+    ranks are covered by the multi-GPU test), alternating with the fused form on the same communicator."""
+    comm = EmulatedCommunicator(world, 640, 4096, torch.bfloat16, DEV)
+    try:
+        for i, rows in enumerate([world * 4, 64, 5, 1, world + 1, 640]):
+            _emulated_case(comm, rows, 4096, torch.bfloat16, seed=300 * world + i, staged=True)
+            _emulated_case(comm, rows, 4096, torch.bfloat16, seed=300 * world + i + 50, staged=False)
+    finally:
+        comm.close()
+    comm = EmulatedCommunicator(2, 16, 16384, torch.float16, DEV)       # two vectors per thread
+    try:
+        _emulated_case(comm, 6, 16384, torch.float16, seed=9, staged=True)
+    finally:
+        comm.close()
 
 
 def test_a_capped_grid_gives_the_same_rows():

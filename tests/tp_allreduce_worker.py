@@ -1,7 +1,7 @@
 """One rank of the multi-GPU all-reduce test (launched by tests/test_allreduce_multigpu.py, one process per GPU).
 
-Every rank fills its partial sums from a seed, runs the fused all-reduce + residual + RMSNorm kernel on the real
-peer-mapped communicator, gathers every rank's partial sums bit for bit (NCCL all_gather) and checks its own
+Every rank fills its partial sums from a seed, runs the fused all-reduce + residual + RMSNorm kernel (and its
+copy-engine form) on the real peer-mapped communicator, gathers every rank's partial sums bit for bit (NCCL all_gather) and checks its own
 residual shard (bit-exact) and the gathered rows (one rounding step) against the CPU oracle; the rows must also be
 identical on every rank.  Prints "TP_ALLREDUCE_OK <rank>" on success.
 """
@@ -28,7 +28,9 @@ def main():
     dtype, hidden, max_rows = torch.bfloat16, 4096, 1024
     comm = TPCommunicator(rank, world, max_rows, hidden, dtype, dev, timeout_ms=2000)
     step = 2.0 ** -7
-    for it, rows in enumerate([512, 64, 5, 1, 1000, 512, 512]):
+    # the fused kernel and the copy-engine form alternate on ONE communicator: they share flags and generations
+    for it, rows in enumerate([512, 64, 5, 1, 1000, 512, 512, 64, 5, 1, 1000, 512]):
+        comm.staged = it >= 5 and it % 2 == 1 or it >= 9
         g = torch.Generator().manual_seed(1000 + it)
         partials = [torch.randn(rows, hidden, generator=g).to(dtype) for _ in range(world)]
         residual = (torch.randn(rows, hidden, generator=g) * 2).to(dtype)

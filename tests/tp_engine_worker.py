@@ -2,7 +2,7 @@
 
 Runs the same requests through the engine at TP = world size (heads and MLP sharded, fused all-reduce + residual +
 RMSNorm over peer memory, residual stream sharded by rows; eager and CUDA-graph decode must agree, and so must
-two prefill waves in flight on two streams (prefill_streams=2) against one stream) and through a
+two prefill waves in flight on two streams (prefill_streams=2, copy-engine all-reduce) against one stream) and through a
 TP = 1 engine built on the same GPU, and compares the final hidden states that reach the LM head at every step in which both
 engines fed the same tokens (a random-init model's logits are nearly flat, so greedy streams may part at a
 near-tie; what must hold is that equal inputs give equal activations up to bf16 rounding).  Prints
@@ -72,18 +72,13 @@ def main():
     dist.all_gather_object(every, tp_tokens)
     assert all(e == every[0] for e in every), "ranks generated different tokens"
     same = sum(a == b for a, b in zip(tp_tokens, one_tokens))
-    # Several prefill waves: with prefill_streams=2 two of them are in flight on two streams, their reductions done
-    # by NCCL reduce-scatter / all-gather on one process group per stream.  The sums differ from the fused
-    # kernel's in rounding only: the hidden states that reach the LM head after each wave must agree.
-    two, two_hidden, (_, waves) = run(world, rank, prompts, steps, max_num_batched_tokens=64, prefill_streams=2)
-    one, one_wave_hidden, (_, none) = run(world, rank, prompts, steps, max_num_batched_tokens=64, prefill_streams=1)
+    # Several prefill waves: with prefill_streams=2 two of them are in flight on two streams, each with its own
+    # communicator whose all-reduces take the copy-engine form (same sums, same roundings as the fused kernel):
+    # the tokens must be those of the one-stream engine.
+    two, _, (_, waves) = run(world, rank, prompts, steps, eager=False, max_num_batched_tokens=64, prefill_streams=2)
+    one, _, (_, none) = run(world, rank, prompts, steps, eager=False, max_num_batched_tokens=64, prefill_streams=1)
     assert waves >= 3 and none == 0, (waves, none)
-    for w in range(waves):
-        a, b = two_hidden[w], one_wave_hidden[w]
-        assert a.shape == b.shape
-        err = float((a - b).abs().max())
-        assert err <= 0.06 * float(b.abs().max()), f"prefill wave {w}: hidden states differ by {err}"
-    assert sum(x[0] == y[0] for x, y in zip(two, one)) >= len(prompts) - 1, "first tokens changed"
+    assert two == one, "two prefill waves in flight changed the tokens"
     dist.barrier()
     dist.destroy_process_group()
     print("TP_ENGINE_OK", rank, compared, f"identical streams {same}/{len(prompts)}", flush=True)
