@@ -729,8 +729,8 @@ prefill_persistent_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gr
         int gk = 0, k = 0;          // KV steps and units so far: ring stages and phases run on across units
         long long u = blockIdx.x;   // first unit; later ones from the counter
         for (;; ++k) {
-          // publish unit k (or the end) for the other roles, then fetch the index of the one after it so that the
-          // atomic's latency passes under this unit's loads
+          // publish unit k (or the end) for the other roles; the index of the one after it is claimed further
+          // down, two KV steps before this unit's loads end
           const int slot = k % kPfUnitRing;
           if (k >= kPfUnitRing) tc::mbar_wait_compact<true>(bar(PB_UEMPTY + slot), ((k / kPfUnitRing) - 1) & 1, abort_flag, p.error_word, 14);
           const bool live = u < total_units && !*abort_flag;
